@@ -31,7 +31,7 @@ KVGroup::KVGroup(const CacheRequest& req, const std::vector<int>& ents, int n_sl
       table((size_t)n_slots * width_, -1) {
     if (on_device) {
         k_pool = DeviceBuffer(entry_bytes() * entries.size());
-        v_pool = DeviceBuffer(entry_bytes() * entries.size());
+        v_pool = DeviceBuffer(value_entry_bytes() * entries.size());
     }
 }
 
@@ -65,7 +65,7 @@ void KVGroup::release_behind(int slot, int length) {
     if (window <= 0) return;
     int* row = &table[(size_t)slot * width];
     const int end = std::min(width, std::max(0, length - window + 1) / PAGE);
-    for (int lp = 0; lp < end; ++lp)
+    for (int lp = kept_pages(); lp < end; ++lp)
         if (row[lp] >= 0) {
             pages.give(row[lp]);
             row[lp] = -1;
@@ -100,12 +100,25 @@ Cache::Cache(const std::map<int, CacheRequest>& requests, int64_t max_tokens, in
     // hold more pages than there are, so the table need not be wider than that; with a window it holds few pages
     // at a time but at any logical place.
     const int seq_pages = std::max(1, (max_seq_tokens + PAGE - 1) / PAGE);
-    typedef std::tuple<int, int, int> Need;
+    typedef std::tuple<int, int, int, int, int> Need;
     std::vector<std::pair<Need, std::vector<int>>> by_need;          // in order of first appearance
+    // a request made of several becomes one request per part, each under a key of its own
+    std::map<int, CacheRequest> flat;
     for (const auto& kv : requests) {
+        if (kv.second.kind != CacheRequest::Several) {
+            flat[kv.first] = kv.second;
+            continue;
+        }
+        parts_of[kv.first] = (int)kv.second.parts.size();
+        for (size_t j = 0; j < kv.second.parts.size(); ++j) {
+            if (kv.second.parts[j].kind == CacheRequest::Several) throw CacheError("a cache request of several parts cannot hold another such");
+            flat[sub_entry(kv.first, (int)j)] = kv.second.parts[j];
+        }
+    }
+    for (const auto& kv : flat) {
         const CacheRequest& r = kv.second;
         if (r.kind == CacheRequest::KV) {
-            const Need need(r.n_kv_heads, r.head_dim, r.window);
+            const Need need(r.n_kv_heads, r.head_dim, r.window, r.value_dim(), r.keep_first);
             auto it = std::find_if(by_need.begin(), by_need.end(), [&](const auto& p) { return p.first == need; });
             if (it == by_need.end()) by_need.emplace_back(need, std::vector<int>{kv.first});
             else it->second.push_back(kv.first);
@@ -121,7 +134,7 @@ Cache::Cache(const std::map<int, CacheRequest>& requests, int64_t max_tokens, in
         }
     }
     for (auto& p : by_need) {
-        const CacheRequest req = requests.at(p.second[0]);
+        const CacheRequest req = flat.at(p.second[0]);
         const int width = req.window > 0 ? seq_pages : std::min(n_pages, seq_pages);
         groups.emplace_back(new KVGroup(req, p.second, max_slots, n_pages, width, dtype, on_device));
         for (int e : p.second) group_of[e] = (int)groups.size() - 1;
@@ -175,13 +188,19 @@ void Cache::table_rows(int g, const std::vector<int>& slot_ids, std::vector<int>
 CacheView Cache::view(int entry, bool write, const std::vector<const int*>& step_tables, const int* seq_slots_dev) const {
     CacheView v;
     v.write = write;
+    auto several = parts_of.find(entry);
+    if (several != parts_of.end()) {
+        v.kind = CacheRequest::Several;
+        for (int j = 0; j < several->second; ++j) v.parts.push_back(view(sub_entry(entry, j), write, step_tables, seq_slots_dev));
+        return v;
+    }
     auto g = group_of.find(entry);
     if (g != group_of.end()) {
         const KVGroup& grp = *groups[g->second];
         const int i = grp.index_of(entry);
         v.kind = CacheRequest::KV;
         v.k_pool = (char*)grp.k_pool.get() + (size_t)i * grp.entry_bytes();
-        v.v_pool = (char*)grp.v_pool.get() + (size_t)i * grp.entry_bytes();
+        v.v_pool = (char*)grp.v_pool.get() + (size_t)i * grp.value_entry_bytes();
         v.pool_pages = grp.n_pages;
         v.block_table = step_tables[g->second];
         v.table_width = grp.width;
@@ -189,6 +208,8 @@ CacheView Cache::view(int entry, bool write, const std::vector<const int*>& step
         v.window = grp.window;
         v.n_kv_heads = grp.request.n_kv_heads;
         v.head_dim = grp.request.head_dim;
+        v.v_head_dim = grp.request.value_dim();
+        v.keep_first = grp.request.keep_first;
         v.dtype = grp.dtype;
         return v;
     }
@@ -210,7 +231,7 @@ int64_t Cache::held_tokens() const {
 
 size_t Cache::bytes() const {
     size_t b = 0;
-    for (const auto& g : groups) b += 2 * g->entry_bytes() * g->entries.size();
+    for (const auto& g : groups) b += (g->entry_bytes() + g->value_entry_bytes()) * g->entries.size();
     for (const auto& kv : states) b += kv.second.slot_bytes * max_slots;
     return b;
 }

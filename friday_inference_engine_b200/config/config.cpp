@@ -126,7 +126,9 @@ Architecture architecture(const std::string& name) {
 std::string architecture_name_of(const Json& d) {
     const Json* a = d.is_object() ? d.find("architectures") : nullptr;
     if (a && a->is_array() && a->size() > 0 && (*a)[0].is_string()) return (*a)[0].as_string();
-    throw ConfigError("config.json: 'architectures' must be a list whose first item names the model class");
+    const Json* one = d.is_object() ? d.find("architecture") : nullptr;           // some designs name it so
+    if (one && one->is_string()) return one->as_string();
+    throw ConfigError("config.json: 'architectures' must be a list whose first item names the model class (or 'architecture' a name)");
 }
 
 Json read_config_file(const std::string& model_dir) {

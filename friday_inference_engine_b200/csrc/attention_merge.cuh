@@ -10,6 +10,7 @@ struct MergeArgs {
     const float* part;   // [rows * nq][splits][hd + 2]
     void* out;           // [rows][nq * hd]
     int rows, nq, hd, splits;
+    float out_scale = 1.0f;   // the merged result is multiplied by this
 };
 
 constexpr int FR_MERGE_PER_LANE = 8;   // head sizes up to 256
@@ -41,7 +42,7 @@ __global__ void __launch_bounds__(128) attention_merge_kernel(MergeArgs p) {
             if (d < p.hd) acc[i] += ps[d] * f;
         }
     }
-    const float inv = l > 0.f ? 1.0f / l : 0.f;
+    const float inv = l > 0.f ? p.out_scale / l : 0.f;
     T* o_row = (T*)p.out + (size_t)item * p.hd;
 #pragma unroll
     for (int i = 0; i < FR_MERGE_PER_LANE; ++i) {

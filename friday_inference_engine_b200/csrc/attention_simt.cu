@@ -2,7 +2,8 @@
 //
 // One kernel serves prompts and decoding, fp32 and bf16 storage, every head size up
 // to 256 (any multiple of 2), any number of heads and groups, full and windowed
-// layers.  A warp owns one (query row, head, split): it walks its range of keys with
+// layers, windows that keep a sequence's first keys in sight, and values whose size
+// differs from the keys'.  A warp owns one (query row, head, split): it walks its range of keys with
 // an online softmax (running maximum m, sum l, weighted values o), the head's
 // dimensions spread over the lanes.  With more than one split the warps write
 // (m, l, o) to a scratch buffer and a second kernel merges them; that keeps many
@@ -15,7 +16,10 @@
 // Geometry of a step: every row carries its sequence (row_seq, an index into the step's
 // block table) and its position (row_pos); it sees the keys of its sequence up to that
 // position.  Keys and values of position j are in page block_table[seq][j / page], row
-// j % page, of pools laid out [pages][page][nkv][hd].
+// j % page, of pools laid out [pages][page][nkv][hd] (keys) and [pages][page][nkv][vd] (values).
+//
+// With a window W and `keep_first` F, row i sees key j if j <= i and (i - j < W or j < F): the keys
+// a warp walks are the kept ones below the window's start followed by the window's.
 #include <math.h>
 
 #include "attention_merge.cuh"
@@ -38,6 +42,8 @@ struct AttnArgs {
     float* part;          // [rows][nq][splits][hd + 2] when splits > 1
     int table_width, page, rows, nq, nkv, hd, q_stride, window, splits;
     float scale;
+    int vd, keep_first;   // size of a value head; keys below keep_first stay visible behind a window
+    float out_scale;      // the result is multiplied by this
 };
 
 template <typename T>
@@ -48,8 +54,8 @@ __global__ void __launch_bounds__(128) attention_kernel(AttnArgs p) {
     const int row = item / p.nq, h = item - row * p.nq;
     const int split = blockIdx.y;
     const int seq = p.row_seq[row];
-    T* o_row = (T*)p.out + (size_t)row * p.nq * p.hd + (size_t)h * p.hd;
-    float* part = p.splits > 1 ? p.part + ((size_t)item * p.splits + split) * (p.hd + 2) : nullptr;
+    T* o_row = (T*)p.out + (size_t)row * p.nq * p.vd + (size_t)h * p.vd;
+    float* part = p.splits > 1 ? p.part + ((size_t)item * p.splits + split) * (p.vd + 2) : nullptr;
 
     float qv[MAX_PER_LANE], acc[MAX_PER_LANE];
 #pragma unroll
@@ -60,10 +66,11 @@ __global__ void __launch_bounds__(128) attention_kernel(AttnArgs p) {
         const int pos = p.row_pos[row];
         const int kvh = h / (p.nq / p.nkv);
         const int lo = p.window > 0 ? max(0, pos - p.window + 1) : 0;
-        const int n = pos - lo + 1;
+        const int kept = min(p.keep_first, lo);         // kept keys below the window's start
+        const int n = kept + pos - lo + 1;
         const int chunk = (n + p.splits - 1) / p.splits;
-        const int j0 = lo + split * chunk;
-        const int j1 = min(j0 + chunk, pos + 1);
+        const int i0 = split * chunk;
+        const int i1 = min(i0 + chunk, n);
         const T* q = (const T*)p.q + (size_t)row * p.q_stride + (size_t)h * p.hd;
 #pragma unroll
         for (int i = 0; i < MAX_PER_LANE; ++i) {
@@ -71,15 +78,16 @@ __global__ void __launch_bounds__(128) attention_kernel(AttnArgs p) {
             qv[i] = d < p.hd ? fr_load(q + d) * p.scale : 0.f;
         }
         const int* table = p.block_table + (size_t)seq * p.table_width;
-        for (int j = j0; j < j1; ++j) {
-            const size_t at = (((size_t)table[j / p.page] * p.page + j % p.page) * p.nkv + kvh) * p.hd;
-            const T* kr = (const T*)p.k_pool + at;
-            const T* vr = (const T*)p.v_pool + at;
+        for (int i = i0; i < i1; ++i) {
+            const int j = i < kept ? i : lo + (i - kept);
+            const size_t at = ((size_t)table[j / p.page] * p.page + j % p.page) * p.nkv + kvh;
+            const T* kr = (const T*)p.k_pool + at * p.hd;
+            const T* vr = (const T*)p.v_pool + at * p.vd;
             float s = 0.f;
 #pragma unroll
-            for (int i = 0; i < MAX_PER_LANE; ++i) {
-                const int d = lane + 32 * i;
-                if (d < p.hd) s = fmaf(qv[i], fr_load(kr + d), s);
+            for (int c = 0; c < MAX_PER_LANE; ++c) {
+                const int d = lane + 32 * c;
+                if (d < p.hd) s = fmaf(qv[c], fr_load(kr + d), s);
             }
             s = fr_warp_sum(s);
             const float m_new = fmaxf(m, s);
@@ -87,53 +95,57 @@ __global__ void __launch_bounds__(128) attention_kernel(AttnArgs p) {
             const float e = expf(s - m_new);
             l = l * alpha + e;
 #pragma unroll
-            for (int i = 0; i < MAX_PER_LANE; ++i) {
-                const int d = lane + 32 * i;
-                if (d < p.hd) acc[i] = acc[i] * alpha + e * fr_load(vr + d);
+            for (int c = 0; c < MAX_PER_LANE; ++c) {
+                const int d = lane + 32 * c;
+                if (d < p.vd) acc[c] = acc[c] * alpha + e * fr_load(vr + d);
             }
             m = m_new;
         }
     }
     if (part == nullptr) {
-        const float inv = l > 0.f ? 1.0f / l : 0.f;
+        const float inv = l > 0.f ? p.out_scale / l : 0.f;
 #pragma unroll
         for (int i = 0; i < MAX_PER_LANE; ++i) {
             const int d = lane + 32 * i;
-            if (d < p.hd) fr_store(o_row + d, acc[i] * inv);
+            if (d < p.vd) fr_store(o_row + d, acc[i] * inv);
         }
     } else {
 #pragma unroll
         for (int i = 0; i < MAX_PER_LANE; ++i) {
             const int d = lane + 32 * i;
-            if (d < p.hd) part[d] = acc[i];
+            if (d < p.vd) part[d] = acc[i];
         }
         if (lane == 0) {
-            part[p.hd] = m;
-            part[p.hd + 1] = l;
+            part[p.vd] = m;
+            part[p.vd + 1] = l;
         }
     }
 }
 
 }  // namespace
 
-// Scratch floats needed for `splits` > 1.
-FR_EXPORT long long attention_simt_scratch_floats(int rows, int nq, int hd, int splits) {
-    return splits > 1 ? (long long)rows * nq * splits * (hd + 2) : 0;
+// Scratch floats needed for `splits` > 1 (vd: the size of a value head).
+FR_EXPORT long long attention_simt_scratch_floats(int rows, int nq, int vd, int splits) {
+    return splits > 1 ? (long long)rows * nq * splits * (vd + 2) : 0;
 }
 
-FR_EXPORT int attention_simt(const void* q, int q_stride, void* out, const void* k_pool, const void* v_pool,
-                             const int* block_table, int table_width, int page, const int* row_seq,
-                             const int* row_pos, int rows, int nq, int nkv, int hd, int window, float scale,
-                             int splits, float* scratch, int dtype, cudaStream_t stream) {
+// vd: size of a value head (the result is [rows][nq * vd]); keep_first: keys below it stay visible behind a window;
+// out_scale multiplies the result.
+FR_EXPORT int attention_simt_masked(const void* q, int q_stride, void* out, const void* k_pool, const void* v_pool,
+                                    const int* block_table, int table_width, int page, const int* row_seq,
+                                    const int* row_pos, int rows, int nq, int nkv, int hd, int vd, int window, int keep_first,
+                                    float scale, float out_scale, int splits, float* scratch, int dtype, cudaStream_t stream) {
     if (rows <= 0) return FR_OK;
     if (hd <= 0 || hd > 32 * MAX_PER_LANE) FR_REFUSE("attention: head size %d is outside 1..%d", hd, 32 * MAX_PER_LANE);
+    if (vd <= 0 || vd > 32 * MAX_PER_LANE) FR_REFUSE("attention: value size %d is outside 1..%d", vd, 32 * MAX_PER_LANE);
     if (nkv <= 0 || nq % nkv != 0) FR_REFUSE("attention: %d heads cannot share %d key/value heads", nq, nkv);
     if (splits < 1 || splits > 65535) FR_REFUSE("attention: %d splits", splits);
     if (splits > 1 && scratch == nullptr) FR_REFUSE("attention: splits need a scratch buffer");
+    if (keep_first < 0) FR_REFUSE("attention: keep_first = %d", keep_first);
     AttnArgs p{q, out, k_pool, v_pool, block_table, row_seq, row_pos, scratch, table_width, page, rows, nq, nkv, hd,
-               q_stride, window, splits, scale};
+               q_stride, window, splits, scale, vd, window > 0 ? keep_first : 0, out_scale};
     const int items = rows * nq;
-    MergeArgs mp{scratch, out, rows, nq, hd, splits};
+    MergeArgs mp{scratch, out, rows, nq, vd, splits, out_scale};
     dim3 grid((items + 3) / 4, splits);
     if (dtype == FR_F32) {
         attention_kernel<float><<<grid, 128, 0, stream>>>(p);
@@ -148,4 +160,12 @@ FR_EXPORT int attention_simt(const void* q, int q_stride, void* out, const void*
     }
     FR_CHECK_LAUNCH("attention merge");
     return FR_OK;
+}
+
+FR_EXPORT int attention_simt(const void* q, int q_stride, void* out, const void* k_pool, const void* v_pool,
+                             const int* block_table, int table_width, int page, const int* row_seq,
+                             const int* row_pos, int rows, int nq, int nkv, int hd, int window, float scale,
+                             int splits, float* scratch, int dtype, cudaStream_t stream) {
+    return attention_simt_masked(q, q_stride, out, k_pool, v_pool, block_table, table_width, page, row_seq, row_pos, rows, nq,
+                                 nkv, hd, hd, window, 0, scale, 1.0f, splits, scratch, dtype, stream);
 }

@@ -1,0 +1,244 @@
+// Routed experts: the choice, and the experts' products for few rows.
+//
+//   route            per row: the `top` largest of the router's logits (the lower index wins a tie), their weights
+//                    (softmax over the chosen logits only, or over all of them), optionally a dense map
+//                    [rows][experts] that holds each chosen expert's weight and zero elsewhere
+//   scale_by_route   act [rows][experts * inner] *= dense[row][column / inner]: after it, one product over all
+//                    experts' down matrices side by side sums exactly the chosen experts
+//   gate_up          for every (row, choice): act = silu(Wg_e h) * (Wu_e h), expert e's rows read where they lie
+//   down_combine     out[row] = residual[row] + sum over choices of weight * (Wd_e act)
+//
+// gate_up and down_combine read only the chosen experts' weights, once per (row, choice): the form for one-token
+// steps, where those bytes are the cost.  With many rows the dense form (all experts through the tensor-core
+// product, scale_by_route, one down product) does more arithmetic but runs on the tensor cores.
+//
+// Router logits, the choice and the weights are fp32.  Gate and up weights are stored row by row in turn
+// (gate 0, up 0, gate 1, ...), expert after expert: [experts * 2 * inner][width]; down: [width][experts * inner].
+#include <math.h>
+
+#include "common.cuh"
+
+FR_EXPORT const char* routed_last_error() { return fr_error_text; }
+
+typedef __nv_bfloat16 bf16;
+
+namespace {
+
+constexpr int ROUTE_PER_LANE = 8;          // up to 256 experts
+
+__global__ void __launch_bounds__(128)
+route_kernel(const float* __restrict__ logits, int ld, int rows, int experts, int top, int softmax_all, int* __restrict__ ids,
+             float* __restrict__ weights, float* __restrict__ dense) {
+    fr_pdl_wait();
+    fr_pdl_launch();
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int row = blockIdx.x * 4 + warp;
+    if (row >= rows) return;
+    float z[ROUTE_PER_LANE];
+    float all_max = -INFINITY;
+#pragma unroll
+    for (int i = 0; i < ROUTE_PER_LANE; ++i) {
+        const int e = lane + 32 * i;
+        z[i] = e < experts ? logits[(size_t)row * ld + e] : -INFINITY;
+        all_max = fmaxf(all_max, z[i]);
+    }
+    all_max = fr_warp_max(all_max);
+    float all_sum = 0.f;
+    if (softmax_all) {
+#pragma unroll
+        for (int i = 0; i < ROUTE_PER_LANE; ++i)
+            if (lane + 32 * i < experts) all_sum += expf(z[i] - all_max);
+        all_sum = fr_warp_sum(all_sum);
+    }
+    if (dense != nullptr)
+        for (int e = lane; e < experts; e += 32) dense[(size_t)row * experts + e] = 0.f;
+    __syncwarp();
+    float first = 0.f, chosen_sum = 0.f;
+    float my_logit = 0.f;                   // lane t keeps the t-th choice
+    int my_id = -1;
+    for (int t = 0; t < top; ++t) {
+        float best = -INFINITY;
+        int best_e = 0x7fffffff;
+#pragma unroll
+        for (int i = 0; i < ROUTE_PER_LANE; ++i) {
+            const int e = lane + 32 * i;
+            if (e < experts && (z[i] > best || (z[i] == best && e < best_e))) {
+                best = z[i];
+                best_e = e;
+            }
+        }
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) {
+            const float ob = __shfl_xor_sync(0xffffffffu, best, o);
+            const int oe = __shfl_xor_sync(0xffffffffu, best_e, o);
+            if (ob > best || (ob == best && oe < best_e)) {
+                best = ob;
+                best_e = oe;
+            }
+        }
+        if (best_e >= experts) best_e = -1;          // no finite logit left (a dead row's garbage)
+        if (t == 0) first = best;
+        chosen_sum += expf(best - first);
+        if (lane == (t & 31)) {
+            my_logit = best;
+            my_id = best_e;
+        }
+#pragma unroll
+        for (int i = 0; i < ROUTE_PER_LANE; ++i)
+            if (lane + 32 * i == best_e) z[i] = -INFINITY;
+    }
+    if (lane < top) {
+        const float w = softmax_all ? expf(my_logit - all_max) / all_sum : expf(my_logit - first) / chosen_sum;
+        ids[(size_t)row * top + lane] = my_id;
+        weights[(size_t)row * top + lane] = w;
+        if (dense != nullptr && my_id >= 0) dense[(size_t)row * experts + my_id] = w;
+    }
+}
+
+template <typename T>
+__global__ void scale_by_route_kernel(T* __restrict__ act, const float* __restrict__ dense, int experts, int inner, long long n) {
+    fr_pdl_wait();
+    fr_pdl_launch();
+    const long long per_row = (long long)experts * inner;
+    for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (long long)gridDim.x * blockDim.x) {
+        const long long row = i / per_row;
+        const int e = (int)((i - row * per_row) / inner);
+        fr_store(act + i, fr_load(act + i) * dense[row * experts + e]);
+    }
+}
+
+// block: one (row, choice) and a tile of `inner`; a warp per inner channel, lanes over the width
+template <typename T>
+__global__ void __launch_bounds__(256)
+gate_up_kernel(const T* __restrict__ h, const int* __restrict__ ids, const T* __restrict__ w_gate_up, T* __restrict__ act,
+               int top, int width, int inner, int per_block) {
+    extern __shared__ float hs[];             // [width]
+    fr_pdl_wait();
+    fr_pdl_launch();
+    const int pair = blockIdx.x;              // row * top + choice
+    const int row = pair / top;
+    const int e = ids[pair];
+    for (int c = threadIdx.x; c < width; c += blockDim.x) hs[c] = fr_load(h + (size_t)row * width + c);
+    __syncthreads();
+    if (e < 0) return;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int f0 = blockIdx.y * per_block;
+    const T* w = w_gate_up + (size_t)e * 2 * inner * width;
+    for (int f = f0 + warp; f < min(f0 + per_block, inner); f += 8) {
+        const T* g = w + (size_t)(2 * f) * width;
+        const T* u = g + width;
+        float sg = 0.f, su = 0.f;
+        for (int c = lane; c < width; c += 32) {
+            sg = fmaf(hs[c], fr_load(g + c), sg);
+            su = fmaf(hs[c], fr_load(u + c), su);
+        }
+        sg = fr_warp_sum(sg);
+        su = fr_warp_sum(su);
+        if (lane == 0) fr_store(act + (size_t)pair * inner + f, sg / (1.0f + expf(-sg)) * su);
+    }
+}
+
+// block: one row and a tile of the width; a warp per output column, lanes over inner
+template <typename T, typename TR>
+__global__ void __launch_bounds__(256)
+down_combine_kernel(const T* __restrict__ act, const int* __restrict__ ids, const float* __restrict__ weights,
+                    const T* __restrict__ w_down, int ld_down, const TR* __restrict__ residual, TR* __restrict__ out, int top,
+                    int width, int inner, int per_block) {
+    extern __shared__ float as[];             // [top][inner]
+    fr_pdl_wait();
+    fr_pdl_launch();
+    const int row = blockIdx.x;
+    for (int i = threadIdx.x; i < top * inner; i += blockDim.x) as[i] = fr_load(act + (size_t)row * top * inner + i);
+    __syncthreads();
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int c0 = blockIdx.y * per_block;
+    for (int c = c0 + warp; c < min(c0 + per_block, width); c += 8) {
+        float total = 0.f;
+        for (int j = 0; j < top; ++j) {
+            const int e = ids[(size_t)row * top + j];
+            if (e < 0) continue;
+            const T* w = w_down + (size_t)c * ld_down + (size_t)e * inner;
+            float s = 0.f;
+            for (int f = lane; f < inner; f += 32) s = fmaf(as[j * inner + f], fr_load(w + f), s);
+            total = fmaf(weights[(size_t)row * top + j], fr_warp_sum(s), total);
+        }
+        if (lane == 0) {
+            const float r = residual != nullptr ? fr_load(residual + (size_t)row * width + c) : 0.f;
+            fr_store(out + (size_t)row * width + c, r + total);
+        }
+    }
+}
+
+}  // namespace
+
+FR_EXPORT int routed_route(const float* logits, int ld, int rows, int experts, int top, int softmax_all, int* ids, float* weights,
+                           float* dense, cudaStream_t stream) {
+    if (rows <= 0) return FR_OK;
+    if (experts < 1 || experts > 32 * ROUTE_PER_LANE) FR_REFUSE("route: %d experts (1 to %d)", experts, 32 * ROUTE_PER_LANE);
+    if (top < 1 || top > experts || top > 32) FR_REFUSE("route: top %d of %d experts (at most 32)", top, experts);
+    FR_CUDA(fr_launch(route_kernel, dim3((rows + 3) / 4), dim3(128), 0, stream, logits, ld, rows, experts, top, softmax_all, ids,
+                      weights, dense));
+    FR_CHECK_LAUNCH("route");
+    return FR_OK;
+}
+
+FR_EXPORT int routed_scale_by_route(void* act, const float* dense, int rows, int experts, int inner, int dtype, cudaStream_t stream) {
+    const long long n = (long long)rows * experts * inner;
+    if (n <= 0) return FR_OK;
+    const long long cap = (long long)(fr_sm_count() > 0 ? fr_sm_count() : 128) * 16;
+    const int blocks = (int)((n + 255) / 256 < cap ? (n + 255) / 256 : cap);
+    if (dtype == FR_F32) FR_CUDA(fr_launch(scale_by_route_kernel<float>, dim3(blocks), dim3(256), 0, stream, (float*)act, dense, experts, inner, n));
+    else if (dtype == FR_BF16) FR_CUDA(fr_launch(scale_by_route_kernel<bf16>, dim3(blocks), dim3(256), 0, stream, (bf16*)act, dense, experts, inner, n));
+    else FR_REFUSE("scale_by_route: unknown dtype %d", dtype);
+    FR_CHECK_LAUNCH("scale_by_route");
+    return FR_OK;
+}
+
+FR_EXPORT int routed_gate_up(const void* h, const int* ids, const void* w_gate_up, void* act, int rows, int top, int width, int inner,
+                             int dtype, cudaStream_t stream) {
+    if (rows <= 0) return FR_OK;
+    const size_t smem = (size_t)width * sizeof(float);
+    if (smem > 200 * 1024) FR_REFUSE("gate_up: width %d does not fit an SM's shared memory", width);
+    const int per_block = inner < 64 ? inner : 64;
+    const dim3 grid(rows * top, (inner + per_block - 1) / per_block);
+    if (grid.y > 65535) FR_REFUSE("gate_up: inner size %d", inner);
+    if (dtype == FR_F32) {
+        if (smem > 48 * 1024) FR_CUDA(cudaFuncSetAttribute(gate_up_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+        FR_CUDA(fr_launch(gate_up_kernel<float>, grid, dim3(256), smem, stream, (const float*)h, ids, (const float*)w_gate_up,
+                          (float*)act, top, width, inner, per_block));
+    } else if (dtype == FR_BF16) {
+        if (smem > 48 * 1024) FR_CUDA(cudaFuncSetAttribute(gate_up_kernel<bf16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+        FR_CUDA(fr_launch(gate_up_kernel<bf16>, grid, dim3(256), smem, stream, (const bf16*)h, ids, (const bf16*)w_gate_up,
+                          (bf16*)act, top, width, inner, per_block));
+    } else {
+        FR_REFUSE("gate_up: unknown dtype %d", dtype);
+    }
+    FR_CHECK_LAUNCH("gate_up");
+    return FR_OK;
+}
+
+// residual and out [rows][width] in res_dtype (fp32 for a 32-bit residual stream); residual may be null.
+FR_EXPORT int routed_down_combine(const void* act, const int* ids, const float* weights, const void* w_down, int ld_down,
+                                  const void* residual, void* out, int res_dtype, int rows, int top, int width, int inner, int dtype,
+                                  cudaStream_t stream) {
+    if (rows <= 0) return FR_OK;
+    const size_t smem = (size_t)top * inner * sizeof(float);
+    if (smem > 200 * 1024) FR_REFUSE("down_combine: top %d x inner %d does not fit an SM's shared memory", top, inner);
+    const int per_block = width < 64 ? width : 64;
+    const dim3 grid(rows, (width + per_block - 1) / per_block);
+    if (grid.y > 65535) FR_REFUSE("down_combine: width %d", width);
+#define DOWN(T, TR)                                                                                                             \
+    do {                                                                                                                        \
+        if (smem > 48 * 1024)                                                                                                   \
+            FR_CUDA(cudaFuncSetAttribute(down_combine_kernel<T, TR>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));  \
+        FR_CUDA(fr_launch(down_combine_kernel<T, TR>, grid, dim3(256), smem, stream, (const T*)act, ids, weights, (const T*)w_down, \
+                          ld_down, (const TR*)residual, (TR*)out, top, width, inner, per_block));                               \
+    } while (0)
+    if (dtype == FR_F32 && res_dtype == FR_F32) DOWN(float, float);
+    else if (dtype == FR_BF16 && res_dtype == FR_F32) DOWN(bf16, float);
+    else if (dtype == FR_BF16 && res_dtype == FR_BF16) DOWN(bf16, bf16);
+    else FR_REFUSE("down_combine: no kernel for dtypes %d and %d", dtype, res_dtype);
+#undef DOWN
+    FR_CHECK_LAUNCH("down_combine");
+    return FR_OK;
+}

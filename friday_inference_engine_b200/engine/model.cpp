@@ -1,9 +1,39 @@
 // DecoderModel: parts from a specification, weights from a source, one pass over rows (model.h).
 #include "friday/model.h"
 
+#include <stdio.h>
+#include <stdlib.h>
+#include <string.h>
+
 #include <set>
 
 namespace friday {
+
+// FRIDAY_DUMP_LAYERS=<folder>: the residual stream after every program entry of every pass is written there as
+// little-endian fp32 [rows, width] (pass<k>_entry<i>.f32), for comparing a model layer by layer with another
+// implementation.  It waits for the device after every layer: for debugging only.
+static void dump_stream(Ops& ops, const Tensor& x, int pass, size_t entry) {
+    const char* dir = getenv("FRIDAY_DUMP_LAYERS");
+    if (!dir || !dir[0]) return;
+    std::vector<float> host((size_t)x.numel());
+    if (x.dtype == DType::F32) {
+        cuda_check(cudaMemcpyAsync(host.data(), x.data, x.bytes(), cudaMemcpyDeviceToHost, ops.stream()), "cudaMemcpyAsync");
+        cuda_check(cudaStreamSynchronize(ops.stream()), "cudaStreamSynchronize");
+    } else {
+        std::vector<uint16_t> raw((size_t)x.numel());
+        cuda_check(cudaMemcpyAsync(raw.data(), x.data, x.bytes(), cudaMemcpyDeviceToHost, ops.stream()), "cudaMemcpyAsync");
+        cuda_check(cudaStreamSynchronize(ops.stream()), "cudaStreamSynchronize");
+        for (size_t i = 0; i < raw.size(); ++i) {
+            const uint32_t bits = (uint32_t)raw[i] << 16;
+            memcpy(&host[i], &bits, 4);
+        }
+    }
+    const std::string path = format("%s/pass%d_entry%zu.f32", dir, pass, entry);
+    if (FILE* f = fopen(path.c_str(), "wb")) {
+        fwrite(host.data(), sizeof(float), host.size(), f);
+        fclose(f);
+    }
+}
 
 class DecoderModel::Root : public Part {
 public:
@@ -17,7 +47,12 @@ DecoderModel::DecoderModel(const ModelSpec& s, DType dtype) : spec(s) {
     owners = spec.cache_entries();
     for (const auto& ls : spec.layers) layers.emplace_back(build<Block>("block", ls, env));
     final_norm.reset(build<Norm>("norm", spec.final_norm, env));
+    if (!spec.embed_norm.kind.empty()) embed_norm.reset(build<Norm>("norm", spec.embed_norm, env));
+    for (const auto& c : spec.program)
+        if (c.inject >= (int)spec.injections.size()) throw ConfigError("a program entry names an injection that the model does not have");
     root_.reset(new Root(env));
+    for (const auto& inj : spec.injections) root_->declare(inj.weight, {spec.width, 2 * spec.width});
+    for (const auto& sh : spec.shared) root_->declare(sh.first, sh.second);
     root_->declare(spec.embedding, {spec.vocab_size, spec.width});
     if (!spec.head.empty()) root_->declare(spec.head, {spec.vocab_size, spec.width});
     if (!spec.head_bias.empty()) root_->declare(spec.head_bias, {spec.vocab_size});
@@ -28,6 +63,7 @@ std::vector<Part::Named> DecoderModel::named_params() {
     root_->named_params("", out);
     for (size_t i = 0; i < layers.size(); ++i) layers[i]->named_params(spec.layers[i].prefix, out);
     final_norm->named_params(spec.final_norm.prefix, out);
+    if (embed_norm) embed_norm->named_params(spec.embed_norm.prefix, out);
     return out;
 }
 
@@ -60,6 +96,7 @@ std::vector<StoredParam> plan_storage(const std::vector<Part::Named>& all, const
         source.info(e.name, &st);
         StoredParam s;
         s.param = e;
+        s.param.decl.shape = st.shape;          // equal but for sizes left to the checkpoint (-1), which it gives here
         s.dtype = storage_dtype(st, e.decl, compute, e.name);
         if (!e.decl.into.empty()) {
             auto key = std::make_pair(e.owner, e.decl.into);
@@ -102,6 +139,13 @@ size_t load_params(const std::vector<StoredParam>& plan, WeightSource& source, O
             bytes += mem->bytes();
             dst = t;
             dst.ld = cols;
+        } else if (e.decl.col0 >= 0) {           // side by side: its own columns of the rows from row0 on
+            const Tensor& big = e.owner->tensor(e.decl.into);
+            if (e.decl.col0 + cols > big.cols())
+                throw ConfigError("parameter '" + e.name + "' does not fit the columns of '" + e.decl.into + "' that it is stacked into");
+            dst = big;
+            dst.data = (char*)big.data + ((size_t)e.decl.row0 * big.ld + (size_t)e.decl.col0) * dtype_size(big.dtype);
+            dst.ld = big.ld;
         } else {
             const Tensor& big = e.owner->tensor(e.decl.into);
             if (big.cols() != cols)
@@ -125,8 +169,16 @@ void DecoderModel::load(WeightSource& source, Ops& ops) {
     embedding = root_->tensor(spec.embedding);
     head = spec.head.empty() ? embedding : root_->tensor(spec.head);       // tied: one copy in memory
     if (!spec.head_bias.empty()) head_bias = root_->tensor(spec.head_bias);
-    for (auto& l : layers) l->finalize(ops);
+    injections.clear();
+    for (const auto& inj : spec.injections) injections.push_back(root_->tensor(inj.weight));
+    std::map<std::string, Tensor> shared;
+    for (const auto& sh : spec.shared) shared[sh.first] = root_->tensor(sh.first);
+    for (auto& l : layers) {
+        l->bind_shared(shared);
+        l->finalize(ops);
+    }
     final_norm->finalize(ops);
+    if (embed_norm) embed_norm->finalize(ops);
 }
 
 DecoderModel::RunOut DecoderModel::run(Ops& ops, const StepContext& ctx, const std::vector<CacheView>& views,
@@ -134,9 +186,16 @@ DecoderModel::RunOut DecoderModel::run(Ops& ops, const StepContext& ctx, const s
     Arena* outer = ops.arena;
     Tensor x = ops.embedding(ctx.tokens, ctx.rows, embedding);
     if (spec.embed_scale != 1.0) ops.scale_rows(x, (float)spec.embed_scale);
+    if (embed_norm) x = embed_norm->forward(ops, x);
+    if (spec.residual_f32 && x.dtype != DType::F32)
+        throw ConfigError("a model with a 32-bit residual stream needs an embedding norm (or a token table) that yields 32-bit rows");
+    const Tensor x0 = x;                    // what injections feed back in; it lives in the caller's arena
     Rows normed;
     bool has_normed = false;
     const size_t n = spec.program.size();
+    static int passes = 0;
+    const bool dumping = getenv("FRIDAY_DUMP_LAYERS") != nullptr;
+    const int pass_no = dumping ? passes++ : 0;
     for (size_t i = 0; i < n; ++i) {
         const LayerCall& call = spec.program[i];
         Block* block = layers[call.layer].get();
@@ -144,12 +203,19 @@ DecoderModel::RunOut DecoderModel::run(Ops& ops, const StepContext& ctx, const s
         Arena* mine = (i + 1 == n) ? outer : layer_arenas[i & 1];
         if (mine != outer) mine->reset();
         ops.arena = mine;
+        if (call.inject >= 0) {
+            // x <- W [x; x0]: both halves in the activation dtype, the sum of products straight into the stream's dtype
+            Tensor both = ops.concat_cast(x, x0, env.dtype);
+            x = ops.linear(Rows(both), injections[(size_t)call.inject], nullptr, nullptr, (int)x.dtype);
+            has_normed = false;
+        }
         Norm* then = nullptr;
         if (i + 1 < n) then = layers[spec.program[i + 1].layer]->first_norm();
         else if (with_final_norm) then = final_norm.get();
         static const CacheView none;
         PartOut o = block->forward(ops, x, has_normed ? &normed : nullptr, ctx, call.cache >= 0 ? views[i] : none, then);
         x = o.x;
+        if (dumping) dump_stream(ops, x, pass_no, i);
         has_normed = o.has_normed && then != nullptr;
         normed = o.normed;
     }

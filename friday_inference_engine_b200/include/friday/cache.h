@@ -12,7 +12,11 @@
 // A group without a window keeps every position of a live sequence.  A group with a
 // window W gives a page back as soon as every position in it is more than W-1 behind the
 // sequence's end: no later query can reach it, so a long sequence holds about
-// W/PAGE + 2 pages of such a group.  Every state request gets a tensor [slots, *shape]
+// W/PAGE + 2 pages of such a group; with `keep_first` F the pages that hold positions below F are
+// kept as long as the sequence lives (its first keys stay visible behind the window).  Values may have a
+// head size of their own (the value pool's rows are then that wide).  A request made of several
+// (a mixer that runs others side by side) is served part by part, each part as if it were an entry of its
+// own.  Every state request gets a tensor [slots, *shape]
 // that is zeroed when a slot is taken.  Lengths, not contents, decide what is valid:
 // slots and pages are used again without being cleared.
 //
@@ -67,6 +71,8 @@ public:
 
     int index_of(int entry) const;
     size_t entry_bytes() const { return (size_t)n_pages * PAGE * request.n_kv_heads * request.head_dim * dtype_size(dtype); }
+    size_t value_entry_bytes() const { return (size_t)n_pages * PAGE * request.n_kv_heads * request.value_dim() * dtype_size(dtype); }
+    int kept_pages() const { return window > 0 ? (request.keep_first + PAGE - 1) / PAGE : 0; }    // never given back behind the window
     int first_needed_page(int start_pos) const;                     // logical page of the earliest key a query at start_pos or later sees
     std::vector<int> pages_missing(int slot, int start_pos, int new_len) const;
     void reserve(int slot, int start_pos, int new_len);
@@ -102,9 +108,12 @@ public:
     FreeList slots;
     std::vector<int> lens;
     std::vector<std::unique_ptr<KVGroup>> groups;
+    // Part j of an entry whose request is made of several is kept under sub_entry(entry, j).
+    static int sub_entry(int entry, int part) { return entry + (part + 1) * (1 << 20); }
     std::map<int, int> group_of;                    // entry -> index into groups
     struct State { std::vector<int64_t> shape; DType dtype; size_t slot_bytes; DeviceBuffer memory; };
     std::map<int, State> states;                    // entry -> [slots, *shape]
+    std::map<int, int> parts_of;                    // entry whose request is made of several -> how many
 
 private:
     bool on_device_;

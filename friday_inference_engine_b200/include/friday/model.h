@@ -32,7 +32,8 @@ public:
     ModelSpec spec;
     BuildEnv env;
     std::vector<std::unique_ptr<Block>> layers;
-    std::unique_ptr<Norm> final_norm;
+    std::unique_ptr<Norm> final_norm, embed_norm;
+    std::vector<Tensor> injections;               // the matrices of ModelSpec::injections
     std::map<int, int> owners;                     // cache entry -> program entry that writes it
     Tensor embedding, head, head_bias;
 

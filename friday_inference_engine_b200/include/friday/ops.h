@@ -114,6 +114,53 @@ public:
     void scale_rows(Tensor& x, float scale);                  // x *= scale (embedding multipliers)
     void finish_logits(Tensor& logits, const Tensor* bias, float scale, float softcap);
 
+    // ---- a residual stream in 32-bit floats beside activations in another dtype
+    // y = x / sqrt(mean(x^2) + eps) * (offset + weight), x and y in dtypes of their own
+    Tensor rmsnorm_to(const Tensor& x, const Tensor& weight, float offset, float eps, DType out_dtype);
+    Tensor concat_cast(const Tensor& a, const Tensor& b, DType out_dtype);            // [a, b] side by side
+    // residual (fp32) + alpha * y (+ beta * z): a new fp32 tensor, or `residual` itself with in_place
+    Tensor add_scaled(const Tensor& residual, const Tensor& y, float alpha, const Tensor* z = nullptr, float beta = 0.f,
+                      bool in_place = false);
+    // residual + alpha * (x weight^T + bias): in the product's epilogue where residual and result share a dtype and
+    // alpha is 1; otherwise the product in 32-bit and add_scaled
+    Tensor linear_residual(const Rows& x, const Tensor& weight, const Tensor* bias, const Tensor& residual, float alpha = 1.0f);
+    // keys [n_kv_heads][head_dim] at column k_off and values [n_kv_heads][v_head_dim] at column v_off of every row of
+    // `src` go to the cache rows of (row_seq, row_pos)
+    void kv_store(const Tensor& src, int64_t k_off, int64_t v_off, const CacheView& view, const StepContext& ctx);
+    // the per-layer token input, in place on the 32-bit stream x: e = table[token][col0 .. col0 + dim);
+    // y = proj (gelu_tanh(gate x) * e); x += y / sqrt(mean(y^2) + eps) * norm
+    void token_input(Tensor& x, const StepContext& ctx, const Tensor& table, int64_t col0, const Tensor& gate, const Tensor& proj,
+                     const Tensor& norm, float eps);
+
+    // ---- mixers with a matrix state per head (csrc/recurrence.cu)
+    // out [n][rows, width]: row + (row before - row) * mu[s]; the row before a step's first comes from the state
+    Tensor shift_mix(const Tensor& h, const std::vector<Tensor>& mu, const CacheView& view, const StepContext& ctx);
+    void tanh_rows(Tensor& x);
+    struct ScanSpec {
+        int heads = 0, dk = 0, dv = 0;
+        int mode = 0;                   // 0: a = sigmoid(z)^(1/tau); 1: a = exp(-exp(z))
+        float q_scale = 1.f, tau = 1.f;
+        int64_t state_offset = 0;       // floats before the heads' matrices in a sequence's state
+        const Tensor* z_bias = nullptr; // [heads * dk]
+        const Tensor* bonus = nullptr;  // [heads * dk]: read the state before the update, with bonus * k v^T for the present token
+        const Tensor* carry = nullptr;  // rows whose last one per sequence is kept at the start of the state
+    };
+    // q, k [rows, >= heads * dk], v [rows, >= heads * dv] (the tensors' row strides are used), z [rows, heads * dk] fp32
+    Tensor state_scan(const Tensor& q, const Tensor& k, const Tensor& v, const Tensor& z, const ScanSpec& spec, const CacheView& view,
+                      const StepContext& ctx);
+    // o [rows, heads * dv] fp32 -> o / rms_head(o) * weight * silu(gate) * out_scale in `dtype`
+    Tensor head_norm_gate(const Tensor& o, const Tensor& gate, const Tensor& weight, bool weight_per_head, int heads, int dv,
+                          float eps, float out_scale, DType dtype, const StepContext& ctx);
+
+    // ---- routed experts (csrc/routed.cu)
+    struct Routing {
+        Tensor ids, weights, dense;     // [rows, top] int32, [rows, top] fp32, [rows, experts] fp32 (if asked for)
+    };
+    Routing route(const Tensor& logits, int top, bool softmax_all, bool with_dense);
+    void scale_by_route(Tensor& act, const Tensor& dense, int experts, int inner);
+    Tensor expert_gate_up(const Tensor& h, const Routing& r, const Tensor& w_gate_up, int top, int inner);
+    Tensor expert_down_combine(const Tensor& act, const Routing& r, const Tensor& w_down, const Tensor& residual, int top, int inner);
+
     // ---- matrix products: x [rows, k] @ weight [n, k]^T (+ bias [n]) (+ residual [rows, n])
     Tensor linear(const Rows& x, const Tensor& weight, const Tensor* bias = nullptr, const Tensor* residual = nullptr,
                   int out_dtype = -1, Tensor* out = nullptr);
@@ -132,8 +179,10 @@ public:
 
     // ---- attention of the step's rows over the paged cache.  q: the buffer that holds the queries, row stride
     // q_stride elements, head h at h * head_dim.
+    // Values of another size than the keys (view.v_head_dim), first keys kept in sight behind a window
+    // (view.keep_first) and a multiplier of the result run on the CUDA-core kernel.
     void attention(const Tensor& q, int64_t q_stride, Tensor& out, const CacheView& view, const StepContext& ctx,
-                   int n_heads, int n_kv_heads, int head_dim, int window, float scale);
+                   int n_heads, int n_kv_heads, int head_dim, int window, float scale, float out_scale = 1.0f);
 
     // ---- sampling: one id per row of logits [rows, vocab] fp32
     void sample(const Tensor& logits, const float* temperature, const int* streams, const int* steps,

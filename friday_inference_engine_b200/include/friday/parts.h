@@ -19,6 +19,8 @@
 //                residual + mix(h).
 //   FeedForward  forward(ops, h, residual, ctx, then) -> residual + f(h).
 //   Block        cache_request() (its mixer's); forward(ops, x, normed, ctx, view, then).
+//   TokenInput   forward(ops, x, ctx): adds to the residual stream something that depends on the row's token
+//                (a per-layer token table, say), in place.
 //
 // `h` is a Rows: either a tensor or rows whose RMSNorm a product has begun and the next
 // product finishes (ops.h); a part that cannot take the latter calls ops.materialize(h).
@@ -66,6 +68,14 @@ struct LayerCall {
     int layer = 0;          // index into ModelSpec::layers; a layer may be named by several entries
     int cache = -1;         // cache entry that the layer's mixer uses in this call; -1: none
     bool write = true;      // false: read an entry that an earlier call filled
+    int inject = -1;        // index into ModelSpec::injections of what happens to the stream right before this call
+};
+
+// x <- W [x; x0] before a layer call: the stream and the embedding's output (after its norm and multiplier) side by
+// side go through one matrix [width, 2 width] (x's columns first).  What a model that runs a span of layers several
+// times uses to feed the input into every pass.
+struct Injection {
+    std::string weight;     // tensor name
 };
 
 struct ModelSpec {
@@ -74,6 +84,14 @@ struct ModelSpec {
     std::string embedding;                      // tensor name of the token table [vocab, width]
     std::vector<PartSpec> layers;               // category "block"
     std::vector<LayerCall> program;
+    PartSpec embed_norm;                        // kind empty: none; a norm applied to the token rows
+    std::vector<Injection> injections;
+    // Tensors that several parts read (a token table that every layer takes a slice of): name -> shape.  The model
+    // holds them once; every part is offered them by name after loading (Part::bind_shared).
+    std::map<std::string, std::vector<int64_t>> shared;
+    // true: the residual stream is kept in 32-bit floats whatever the activations' dtype; norms read it and write
+    // the activation dtype, products add into it in 32-bit.
+    bool residual_f32 = false;
     PartSpec final_norm;
     std::string head;                           // tensor name of the head [vocab, width]; empty: the token table
     std::string head_bias;                      // tensor name of a bias [vocab] added to the logits; empty: none
@@ -88,12 +106,17 @@ struct ModelSpec {
 
 // ---- what a mixer may ask of the cache
 struct CacheRequest {
-    enum Kind { None, KV, State } kind = None;
+    enum Kind { None, KV, State, Several } kind = None;
     int n_kv_heads = 0, head_dim = 0, window = 0;    // KV: keys and values for every position, or the last `window`
+    int v_head_dim = 0;                              // KV: size of a value head (0: the keys')
+    int keep_first = 0;                              // KV with a window: positions below this stay visible (and held) for good
     std::vector<int64_t> state_shape;                // State: a tensor of this shape per sequence, zero at its start
     DType state_dtype = DType::F32;
-    static CacheRequest kv(int n_kv_heads, int head_dim, int window = 0);
+    std::vector<CacheRequest> parts;                 // Several: what each of a mixer's sub-mixers asks for, in its order
+    static CacheRequest kv(int n_kv_heads, int head_dim, int window = 0, int v_head_dim = 0, int keep_first = 0);
     static CacheRequest state(const std::vector<int64_t>& shape, DType dtype = DType::F32);
+    static CacheRequest several(const std::vector<CacheRequest>& parts);
+    int value_dim() const { return v_head_dim > 0 ? v_head_dim : head_dim; }
 };
 
 // ---- what the cache hands a mixer for one layer call
@@ -106,10 +129,13 @@ struct CacheView {
     int pool_pages = 0;
     const int* block_table = nullptr;      // [n_seqs][table_width], -1 where the sequence holds no page
     int table_width = 0, page_size = 0, window = 0, n_kv_heads = 0, head_dim = 0;
+    int v_head_dim = 0, keep_first = 0;    // values [pages][page_size][kv heads][v_head_dim]; see CacheRequest
     DType dtype = DType::F32;
     // State: state[slot] is the sequence's own tensor
     Tensor state;                          // [slots, ...]
     const int* seq_slots = nullptr;        // device: slot of every sequence of the step
+    // Several: one view per part of the request
+    std::vector<CacheView> parts;
 };
 
 // ---- the geometry of one pass of the step function; parts read it, nothing writes it once it is built
@@ -132,18 +158,26 @@ struct BuildEnv {
 };
 
 struct ParamDecl {
-    std::vector<int64_t> shape;
+    std::vector<int64_t> shape;     // -1: a size that the checkpoint gives (random weights need every size)
     bool integer = false;    // kept as int32; otherwise in the activation dtype unless stored in 32-bit
     bool one = false;        // random-weights mode: 1 + N(0, 0.02) (norm weights) instead of N(0, 0.02)
     // A parameter may be loaded straight into rows of a larger tensor that the part declared with
     // declare_stacked (q, k and v under one another; gate and up row by row in turn): row r of the parameter
     // becomes row row0 + r * row_step of `into`.  The stacked tensor is 32-bit if any of its members is stored so.
+    // With `col0` >= 0 the parameter instead fills the columns [col0, col0 + its own) of the rows from row0 on
+    // (matrices side by side).
     std::string into;
-    int64_t row0 = 0, row_step = 1;
+    int64_t row0 = 0, row_step = 1, col0 = -1;
     ParamDecl& stack(const std::string& name, int64_t first_row, int64_t step = 1) {
         into = name;
         row0 = first_row;
         row_step = step;
+        return *this;
+    }
+    ParamDecl& stack_columns(const std::string& name, int64_t first_col, int64_t first_row = 0) {
+        into = name;
+        row0 = first_row;
+        col0 = first_col;
         return *this;
     }
 };
@@ -164,6 +198,8 @@ public:
     void set_tensor(const std::string& name, const Tensor& t) { tensors[name] = t; }
     const Tensor& tensor(const std::string& name) const;                 // KernelError if unset
     virtual void finalize(Ops& ops);                                       // default: the children's
+    // Offered once after loading: the model's shared tensors by name (ModelSpec::shared).  Default: the children's.
+    virtual void bind_shared(const std::map<std::string, Tensor>& shared);
 
     struct Named { std::string name; Part* owner; std::string local; ParamDecl decl; };
     void named_params(const std::string& prefix, std::vector<Named>& out);
@@ -202,6 +238,8 @@ struct PartOut;
 class Mixer : public Part {
 public:
     using Part::Part;
+    // forward returns residual + out_scale * mix(h); a mixer that runs others side by side sets its members' scales.
+    float out_scale = 1.0f;
     virtual CacheRequest cache_request() const { return CacheRequest(); }
     virtual PartOut forward(Ops& ops, const Rows& h, const Tensor& residual, const StepContext& ctx,
                             const CacheView& view, Norm* then) = 0;
@@ -211,6 +249,13 @@ class FeedForward : public Part {
 public:
     using Part::Part;
     virtual PartOut forward(Ops& ops, const Rows& h, const Tensor& residual, const StepContext& ctx, Norm* then) = 0;
+};
+
+class TokenInput : public Part {
+public:
+    using Part::Part;
+    // x [rows, width] is the residual stream after the layer's feed-forward; changed in place.
+    virtual void forward(Ops& ops, Tensor& x, const StepContext& ctx) = 0;
 };
 
 class Block : public Part {

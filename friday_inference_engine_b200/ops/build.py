@@ -4,7 +4,8 @@ CUDA kernels under csrc/ for sm_100a, one shared library per kernel file.
 libfriday_engine.so holds everything between a model folder and its logits:
 configuration, weights, parts, cache, step function, decoder, generation loop.  It opens
 the kernel libraries itself, each when it is first needed; a kernel family (rowwise,
-gemm_simt, gemm_tc, attention_simt, attention_mma, attention_tc, sampling) is one .cu
+gemm_simt, gemm_tc, attention_simt, attention_mma, attention_tc, sampling, residual,
+recurrence, routed) is one .cu
 file with a C interface and becomes one .so beside it
 (friday_inference_engine_b200/_build/).  A library is compiled when it is first needed
 and was not made from the present sources, so a run compiles what its model and dtype
@@ -29,7 +30,8 @@ CSRC = os.path.join(os.path.dirname(_HERE), "csrc")
 ARCH_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a"]
 NVCC_FLAGS = ["-O3", "-std=c++17", "-lineinfo", "--shared", "-Xcompiler", "-fPIC,-fvisibility=hidden",
               "--expt-relaxed-constexpr"]
-FAMILIES = ("rowwise", "gemm_simt", "attention_simt", "sampling", "gemm_tc", "attention_mma", "attention_tc")
+FAMILIES = ("rowwise", "gemm_simt", "attention_simt", "sampling", "gemm_tc", "attention_mma", "attention_tc", "residual",
+            "recurrence", "routed")
 PACKAGE = os.path.dirname(_HERE)
 SOURCE_DIRS = ("config", "weights", "parts", "cache", "engine", "sampling", "ops")
 INCLUDE = os.path.join(PACKAGE, "include")

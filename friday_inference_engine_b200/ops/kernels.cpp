@@ -96,7 +96,17 @@ FAMILY(Rowwise, rowwise, "rowwise",
        resolve(h, fam, "rowwise_random_normal", t.random_normal);)
 FAMILY(GemmSimt, gemm_simt, "gemm_simt", resolve(h, fam, "gemm_simt", t.gemm);)
 FAMILY(GemmTc, gemm_tc, "gemm_tc", resolve(h, fam, "gemm_tc_fused", t.fused); resolve(h, fam, "gemm_tc_plan", t.plan);)
-FAMILY(AttentionSimt, attention_simt, "attention_simt", resolve(h, fam, "attention_simt", t.run);)
+FAMILY(AttentionSimt, attention_simt, "attention_simt", resolve(h, fam, "attention_simt", t.run);
+       resolve(h, fam, "attention_simt_masked", t.masked);)
+FAMILY(Residual, residual, "residual", resolve(h, fam, "residual_norm_cast", t.norm_cast);
+       resolve(h, fam, "residual_concat_cast", t.concat_cast); resolve(h, fam, "residual_add_scaled", t.add_scaled);
+       resolve(h, fam, "residual_kv_store", t.kv_store); resolve(h, fam, "residual_token_input", t.token_input);)
+FAMILY(Recurrence, recurrence, "recurrence", resolve(h, fam, "recurrence_shift_mix", t.shift_mix);
+       resolve(h, fam, "recurrence_tanh_rows", t.tanh_rows); resolve(h, fam, "recurrence_scan", t.scan);
+       resolve(h, fam, "recurrence_head_norm_gate", t.head_norm_gate);)
+FAMILY(Routed, routed, "routed", resolve(h, fam, "routed_route", t.route);
+       resolve(h, fam, "routed_scale_by_route", t.scale_by_route); resolve(h, fam, "routed_gate_up", t.gate_up);
+       resolve(h, fam, "routed_down_combine", t.down_combine);)
 FAMILY(AttentionMma, attention_mma, "attention_mma", resolve(h, fam, "attention_mma", t.run);
        resolve(h, fam, "attention_mma_clusters_at_once", t.clusters_at_once);)
 FAMILY(AttentionTc, attention_tc, "attention_tc", resolve(h, fam, "attention_tc", t.run);)

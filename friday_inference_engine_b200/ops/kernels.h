@@ -45,6 +45,37 @@ struct AttentionSimt {
     last_error_fn last_error;
     int (*run)(const void*, int, void*, const void*, const void*, const int*, int, int, const int*, const int*, int, int, int,
                int, int, float, int, float*, int, cudaStream_t);
+    int (*masked)(const void*, int, void*, const void*, const void*, const int*, int, int, const int*, const int*, int, int, int,
+                  int, int, int, int, float, float, int, float*, int, cudaStream_t);
+};
+struct Residual {
+    last_error_fn last_error;
+    int (*norm_cast)(const void*, int, const void*, int, float, void*, int, int, int, float, cudaStream_t);
+    int (*concat_cast)(const void*, const void*, int, void*, int, int, int, int, cudaStream_t);
+    int (*add_scaled)(const float*, const void*, float, const void*, float, int, float*, long long, cudaStream_t);
+    int (*kv_store)(const void*, int, int, int, int, int, int, const int*, const int*, void*, void*, const int*, int, int, int, int,
+                    cudaStream_t);
+    int (*token_input)(float*, const int*, const int*, const void*, int, int, int, const void*, const void*, const void*, int, int,
+                       int, int, float, int, cudaStream_t);
+};
+struct Recurrence {
+    last_error_fn last_error;
+    int (*shift_mix)(const void*, void*, const void* const*, int, int, const float*, long long, const int*, const int*, const int*,
+                     int, int, int, cudaStream_t);
+    int (*tanh_rows)(void*, long long, int, cudaStream_t);
+    int (*scan)(const void*, int, const void*, int, const void*, int, const float*, const void*, int, const void*, int, float*,
+                float*, long long, long long, const void*, int, const int*, const int*, const int*, const int*, int, int, int, int,
+                int, int, float, float, int, cudaStream_t);
+    int (*head_norm_gate)(const float*, const void*, int, void*, const void*, int, int, const int*, int, int, int, float, float, int,
+                          cudaStream_t);
+};
+struct Routed {
+    last_error_fn last_error;
+    int (*route)(const float*, int, int, int, int, int, int*, float*, float*, cudaStream_t);
+    int (*scale_by_route)(void*, const float*, int, int, int, int, cudaStream_t);
+    int (*gate_up)(const void*, const int*, const void*, void*, int, int, int, int, int, cudaStream_t);
+    int (*down_combine)(const void*, const int*, const float*, const void*, int, const void*, void*, int, int, int, int, int, int,
+                        cudaStream_t);
 };
 struct AttentionMma {
     last_error_fn last_error;
@@ -71,6 +102,9 @@ const AttentionSimt& attention_simt();
 const AttentionMma& attention_mma();
 const AttentionTc& attention_tc();
 const Sampling& sampling();
+const Residual& residual();
+const Recurrence& recurrence();
+const Routed& routed();
 
 // Called with a family's name when its library is missing; returns 0 when it has built it.
 typedef int (*builder_fn)(const char* family);

@@ -188,6 +188,182 @@ void Ops::finish_logits(Tensor& logits, const Tensor* bias, float scale, float s
          "finish_logits");
 }
 
+// ------------------------------------------------------------------ a 32-bit residual stream
+Tensor Ops::rmsnorm_to(const Tensor& x, const Tensor& weight, float offset, float eps, DType out_dtype) {
+    if (!x.contiguous() || weight.numel() != x.cols())
+        throw KernelError(format("rmsnorm: rows of %lld columns (contiguous: %d), weight of %lld", (long long)x.cols(),
+                                 (int)x.contiguous(), (long long)weight.numel()));
+    Tensor o = alloc(out_dtype, x.rows(), x.cols());
+    const auto& k = kernels::residual();
+    Timed t(*this, Other);
+    call(launches_, k, k.norm_cast(x.data, code(x.dtype), weight.data, code(weight.dtype), offset, o.data, code(out_dtype),
+                                   (int)x.rows(), (int)x.cols(), eps, stream_), "norm_cast");
+    return o;
+}
+
+Tensor Ops::concat_cast(const Tensor& a, const Tensor& b, DType out_dtype) {
+    if (!a.contiguous() || !b.contiguous() || a.rows() != b.rows() || a.dtype != b.dtype)
+        throw KernelError("concat_cast: two contiguous tensors of equal rows and dtype");
+    Tensor o = alloc(out_dtype, a.rows(), a.cols() + b.cols());
+    const auto& k = kernels::residual();
+    Timed t(*this, Other);
+    call(launches_, k, k.concat_cast(a.data, b.data, code(a.dtype), o.data, code(out_dtype), (int)a.rows(), (int)a.cols(),
+                                     (int)b.cols(), stream_), "concat_cast");
+    return o;
+}
+
+Tensor Ops::add_scaled(const Tensor& residual, const Tensor& y, float alpha, const Tensor* z, float beta, bool in_place) {
+    if (residual.dtype != DType::F32 || !residual.contiguous() || !y.contiguous() || y.numel() != residual.numel() ||
+        (z && (z->dtype != y.dtype || !z->contiguous() || z->numel() != y.numel())))
+        throw KernelError("add_scaled: a contiguous 32-bit residual and addends of its size");
+    Tensor o = in_place ? residual : alloc(DType::F32, residual.rows(), residual.cols());
+    const auto& k = kernels::residual();
+    Timed t(*this, Other);
+    call(launches_, k, k.add_scaled((const float*)residual.data, y.data, alpha, z ? z->data : nullptr, beta, code(y.dtype),
+                                    (float*)o.data, (long long)residual.numel(), stream_), "add_scaled");
+    return o;
+}
+
+Tensor Ops::linear_residual(const Rows& x, const Tensor& weight, const Tensor* bias, const Tensor& residual, float alpha) {
+    if (alpha == 1.0f && residual.dtype == x.t.dtype) return linear(x, weight, bias, &residual);
+    if (residual.dtype != DType::F32) throw KernelError("linear_residual: a multiplier needs a 32-bit residual stream");
+    if (alpha == 1.0f && x.t.dtype == DType::F32) return linear(x, weight, bias, &residual, (int)DType::F32);
+    Tensor y = linear(x, weight, bias, nullptr, (int)DType::F32);
+    return add_scaled(residual, y, alpha);
+}
+
+void Ops::kv_store(const Tensor& src, int64_t k_off, int64_t v_off, const CacheView& view, const StepContext& ctx) {
+    if (view.kind != CacheRequest::KV || !view.k_pool) throw KernelError("kv_store needs a view of keys and values");
+    if (!view.write) return;
+    if (view.dtype != src.dtype) throw KernelError("kv_store: the cache's dtype differs from the rows'");
+    const int vd = view.v_head_dim > 0 ? view.v_head_dim : view.head_dim;
+    const auto& k = kernels::residual();
+    Timed t(*this, Other);
+    call(launches_, k, k.kv_store(src.data, (int)src.ld, (int)k_off, (int)v_off, view.n_kv_heads, view.head_dim, vd, ctx.row_seq,
+                                  ctx.row_pos, view.k_pool, view.v_pool, view.block_table, view.table_width, view.page_size,
+                                  (int)src.rows(), code(src.dtype), stream_), "kv_store");
+}
+
+void Ops::token_input(Tensor& x, const StepContext& ctx, const Tensor& table, int64_t col0, const Tensor& gate, const Tensor& proj,
+                      const Tensor& norm, float eps) {
+    const int64_t dim = gate.rows();
+    if (x.dtype != DType::F32 || !x.contiguous()) throw KernelError("token_input: the residual stream must be contiguous 32-bit floats");
+    if (gate.cols() != x.cols() || proj.rows() != x.cols() || proj.cols() != dim || norm.numel() != x.cols() ||
+        col0 < 0 || col0 + dim > table.cols() || gate.dtype != table.dtype || proj.dtype != table.dtype)
+        throw KernelError("token_input: gate [dim, width], proj [width, dim], norm [width] and a table slice of dim columns, one dtype");
+    const auto& k = kernels::residual();
+    Timed t(*this, Other);
+    call(launches_, k, k.token_input((float*)x.data, ctx.tokens, ctx.row_seq, table.data, (int)table.ld, (int)col0, (int)table.rows(),
+                                     gate.data, proj.data, norm.data, code(norm.dtype), (int)x.rows(), (int)x.cols(), (int)dim, eps,
+                                     code(table.dtype), stream_), "token_input");
+}
+
+// ------------------------------------------------------------------ mixers with a matrix state
+Tensor Ops::shift_mix(const Tensor& h, const std::vector<Tensor>& mu, const CacheView& view, const StepContext& ctx) {
+    if (view.kind != CacheRequest::State || !view.state.defined()) throw KernelError("shift_mix needs a state view");
+    if (!h.contiguous() || mu.empty() || mu.size() > 8) throw KernelError("shift_mix: contiguous rows and 1 to 8 mixes");
+    const void* ptrs[8] = {nullptr};
+    for (size_t i = 0; i < mu.size(); ++i) {
+        if (mu[i].numel() != h.cols() || mu[i].dtype != mu[0].dtype) throw KernelError("shift_mix: every mix is a vector of the width, one dtype");
+        ptrs[i] = mu[i].data;
+    }
+    Tensor out = alloc(h.dtype, (int64_t)mu.size() * h.rows(), h.cols());
+    const long long stride = view.state.numel() / view.state.shape[0];
+    const auto& k = kernels::recurrence();
+    Timed t(*this, Other);
+    call(launches_, k, k.shift_mix(h.data, out.data, ptrs, (int)mu.size(), code(mu[0].dtype), (const float*)view.state.data, stride,
+                                   ctx.row_seq, ctx.seq_start, view.seq_slots, (int)h.rows(), (int)h.cols(), code(h.dtype), stream_),
+         "shift_mix");
+    return out;
+}
+
+void Ops::tanh_rows(Tensor& x) {
+    if (!x.contiguous()) throw KernelError("tanh_rows: rows must be contiguous");
+    const auto& k = kernels::recurrence();
+    Timed t(*this, Other);
+    call(launches_, k, k.tanh_rows(x.data, (long long)x.numel(), code(x.dtype), stream_), "tanh_rows");
+}
+
+Tensor Ops::state_scan(const Tensor& q, const Tensor& kk, const Tensor& v, const Tensor& z, const ScanSpec& s, const CacheView& view,
+                       const StepContext& ctx) {
+    if (view.kind != CacheRequest::State || !view.state.defined() || view.state.dtype != DType::F32)
+        throw KernelError("state_scan needs a 32-bit state view");
+    if (q.dtype != kk.dtype || q.dtype != v.dtype || z.dtype != DType::F32 || !z.contiguous() || z.cols() != (int64_t)s.heads * s.dk)
+        throw KernelError("state_scan: q, k, v of one dtype and fp32 decays [rows, heads * dk]");
+    const long long stride = view.state.numel() / view.state.shape[0];
+    if (s.state_offset + (long long)s.heads * s.dk * s.dv > stride) throw KernelError("state_scan: the state is smaller than the heads' matrices");
+    Tensor out = alloc(DType::F32, q.rows(), (int64_t)s.heads * s.dv);
+    const auto& k = kernels::recurrence();
+    Timed t(*this, Attention);
+    call(launches_, k,
+         k.scan(q.data, (int)q.ld, kk.data, (int)kk.ld, v.data, (int)v.ld, (const float*)z.data, s.z_bias ? s.z_bias->data : nullptr,
+                s.z_bias ? code(s.z_bias->dtype) : 0, s.bonus ? s.bonus->data : nullptr, s.bonus ? code(s.bonus->dtype) : 0,
+                (float*)out.data, (float*)view.state.data, stride, (long long)s.state_offset, s.carry ? s.carry->data : nullptr,
+                s.carry ? (int)s.carry->cols() : 0, ctx.row_seq, ctx.seq_start, ctx.seq_qlen, view.seq_slots, ctx.n_seqs,
+                ctx.max_q_len, s.heads, s.dk, s.dv, s.mode, s.q_scale, s.tau, code(q.dtype), stream_),
+         "scan");
+    return out;
+}
+
+Tensor Ops::head_norm_gate(const Tensor& o, const Tensor& gate, const Tensor& weight, bool weight_per_head, int heads, int dv,
+                           float eps, float out_scale, DType dtype, const StepContext& ctx) {
+    if (o.dtype != DType::F32 || !o.contiguous() || o.cols() != (int64_t)heads * dv || gate.dtype != dtype ||
+        weight.numel() != (weight_per_head ? (int64_t)heads * dv : (int64_t)dv))
+        throw KernelError("head_norm_gate: fp32 rows [rows, heads * dv], a gate in the result's dtype, a weight per channel");
+    Tensor out = alloc(dtype, o.rows(), o.cols());
+    const auto& k = kernels::recurrence();
+    Timed t(*this, Other);
+    call(launches_, k, k.head_norm_gate((const float*)o.data, gate.data, (int)gate.ld, out.data, weight.data, code(weight.dtype),
+                                        weight_per_head ? 1 : 0, ctx.row_seq, (int)o.rows(), heads, dv, eps, out_scale, code(dtype),
+                                        stream_), "head_norm_gate");
+    return out;
+}
+
+// ------------------------------------------------------------------ routed experts
+Ops::Routing Ops::route(const Tensor& logits, int top, bool softmax_all, bool with_dense) {
+    if (logits.dtype != DType::F32) throw KernelError("route: router logits are float32");
+    Routing r;
+    const int64_t rows = logits.rows(), experts = logits.cols();
+    r.ids = Tensor::make(arena->alloc((size_t)rows * top * sizeof(int)), DType::I32, {rows, (int64_t)top});
+    r.weights = alloc(DType::F32, rows, top);
+    if (with_dense) r.dense = alloc(DType::F32, rows, experts);
+    const auto& k = kernels::routed();
+    Timed t(*this, Other);
+    call(launches_, k, k.route((const float*)logits.data, (int)logits.ld, (int)rows, (int)experts, top, softmax_all ? 1 : 0,
+                               (int*)r.ids.data, (float*)r.weights.data, with_dense ? (float*)r.dense.data : nullptr, stream_), "route");
+    return r;
+}
+
+void Ops::scale_by_route(Tensor& act, const Tensor& dense, int experts, int inner) {
+    if (!act.contiguous() || act.cols() != (int64_t)experts * inner || dense.rows() != act.rows()) throw KernelError("scale_by_route: shapes");
+    const auto& k = kernels::routed();
+    Timed t(*this, Other);
+    call(launches_, k, k.scale_by_route(act.data, (const float*)dense.data, (int)act.rows(), experts, inner, code(act.dtype), stream_),
+         "scale_by_route");
+}
+
+Tensor Ops::expert_gate_up(const Tensor& h, const Routing& r, const Tensor& w_gate_up, int top, int inner) {
+    if (!h.contiguous() || h.dtype != w_gate_up.dtype || !w_gate_up.contiguous() || w_gate_up.cols() != h.cols())
+        throw KernelError("expert_gate_up: rows and stacked gate/up weights of one dtype and width");
+    Tensor act = alloc(h.dtype, h.rows() * top, inner);
+    const auto& k = kernels::routed();
+    Timed t(*this, Product);
+    call(launches_, k, k.gate_up(h.data, (const int*)r.ids.data, w_gate_up.data, act.data, (int)h.rows(), top, (int)h.cols(), inner,
+                                 code(h.dtype), stream_), "gate_up");
+    return act;
+}
+
+Tensor Ops::expert_down_combine(const Tensor& act, const Routing& r, const Tensor& w_down, const Tensor& residual, int top, int inner) {
+    if (act.dtype != w_down.dtype) throw KernelError("expert_down_combine: activations and weights of one dtype");
+    Tensor out = alloc(residual.dtype, residual.rows(), residual.cols());
+    const auto& k = kernels::routed();
+    Timed t(*this, Product);
+    call(launches_, k, k.down_combine(act.data, (const int*)r.ids.data, (const float*)r.weights.data, w_down.data, (int)w_down.ld,
+                                      residual.data, out.data, code(residual.dtype), (int)residual.rows(), top, (int)residual.cols(),
+                                      inner, code(act.dtype), stream_), "down_combine");
+    return out;
+}
+
 // ------------------------------------------------------------------ matrix products
 bool Ops::tensor_core_ok(const Tensor& x, const Tensor& weight, const Tensor& out, const Tensor* residual) const {
     (void)residual;
@@ -481,8 +657,26 @@ int Ops::decode_splits(int n_seqs, int n_heads, int n_kv_heads, int head_dim, in
 }
 
 void Ops::attention(const Tensor& q, int64_t q_stride, Tensor& out, const CacheView& view, const StepContext& ctx,
-                    int n_heads, int n_kv_heads, int head_dim, int window, float scale) {
+                    int n_heads, int n_kv_heads, int head_dim, int window, float scale, float out_scale) {
     if (view.kind != CacheRequest::KV || !view.k_pool) throw KernelError("attention needs a view of keys and values");
+    const int vd = view.v_head_dim > 0 ? view.v_head_dim : head_dim;
+    const int keep = window > 0 ? view.keep_first : 0;
+    if (vd != head_dim || keep > 0 || out_scale != 1.0f) {
+        // the general form: CUDA cores, fp32 arithmetic
+        const int rows_ = (int)out.rows();
+        int kv_reach = ctx.max_kv_len;
+        if (window > 0 && window + keep < kv_reach) kv_reach = window + keep;
+        const int splits = attention_splits(rows_, n_heads, kv_reach);
+        float* scratch = splits > 1 ? scratch_floats((int64_t)rows_ * n_heads * splits * (vd + 2)) : nullptr;
+        const auto& k = kernels::attention_simt();
+        Timed t(*this, Attention);
+        call(launches_, k,
+             k.masked(q.data, (int)q_stride, out.data, view.k_pool, view.v_pool, view.block_table, view.table_width, view.page_size,
+                      ctx.row_seq, ctx.row_pos, rows_, n_heads, n_kv_heads, head_dim, vd, window, keep, scale, out_scale, splits,
+                      scratch, code(out.dtype), stream_),
+             "attention_simt_masked");
+        return;
+    }
     const bool geometry = ctx.seq_start != nullptr;
     const bool hd_ok = head_dim % 16 == 0 && head_dim >= 16 && head_dim <= 128 && view.page_size == 64;
     const int rows = (int)out.rows();

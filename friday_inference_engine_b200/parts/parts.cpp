@@ -38,12 +38,21 @@ std::map<int, int> ModelSpec::cache_entries() const {
     return owners;
 }
 
-CacheRequest CacheRequest::kv(int n_kv_heads, int head_dim, int window) {
+CacheRequest CacheRequest::kv(int n_kv_heads, int head_dim, int window, int v_head_dim, int keep_first) {
     CacheRequest r;
     r.kind = KV;
     r.n_kv_heads = n_kv_heads;
     r.head_dim = head_dim;
     r.window = window;
+    r.v_head_dim = v_head_dim == head_dim ? 0 : v_head_dim;
+    r.keep_first = window > 0 ? keep_first : 0;
+    return r;
+}
+
+CacheRequest CacheRequest::several(const std::vector<CacheRequest>& parts) {
+    CacheRequest r;
+    r.kind = Several;
+    r.parts = parts;
     return r;
 }
 
@@ -76,6 +85,10 @@ void Part::finalize(Ops& ops) {
     for (auto& c : children_) c.second->finalize(ops);
 }
 
+void Part::bind_shared(const std::map<std::string, Tensor>& shared) {
+    for (auto& c : children_) c.second->bind_shared(shared);
+}
+
 void Part::named_params(const std::string& pre, std::vector<Named>& out) {
     for (auto& p : params) out.push_back(Named{pre + p.first, this, p.first, p.second});
     for (auto& c : children_) c.second->named_params(pre + c.first, out);
@@ -83,7 +96,7 @@ void Part::named_params(const std::string& pre, std::vector<Named>& out) {
 
 // ------------------------------------------------------------------ registry
 namespace {
-const char* kCategories[] = {"norm", "position", "mixer", "feed_forward", "block"};
+const char* kCategories[] = {"norm", "position", "mixer", "feed_forward", "token_input", "block"};
 std::mutex& reg_mutex() { static std::mutex m; return m; }
 std::map<std::string, std::map<std::string, PartFactory>>& reg() {
     static std::map<std::string, std::map<std::string, PartFactory>> r;
@@ -98,14 +111,14 @@ bool known_category(const std::string& c) {
 
 void register_part(const std::string& category, const std::string& kind, PartFactory factory) {
     if (!known_category(category))
-        throw ConfigError("unknown part category '" + category + "' (have: norm, position, mixer, feed_forward, block)");
+        throw ConfigError("unknown part category '" + category + "' (have: norm, position, mixer, feed_forward, token_input, block)");
     std::lock_guard<std::mutex> lock(reg_mutex());
     reg()[category][kind] = std::move(factory);
 }
 
 std::vector<std::string> registered_parts(const std::string& category) {
     if (!known_category(category))
-        throw ConfigError("unknown part category '" + category + "' (have: norm, position, mixer, feed_forward, block)");
+        throw ConfigError("unknown part category '" + category + "' (have: norm, position, mixer, feed_forward, token_input, block)");
     std::lock_guard<std::mutex> lock(reg_mutex());
     std::vector<std::string> out;
     for (const auto& kv : reg()[category]) out.push_back(kv.first);
@@ -146,18 +159,32 @@ public:
         if (!eps || !eps->is_number()) throw ConfigError("rmsnorm needs 'eps'");
         eps_ = (float)eps->as_double();
         width_ = s.params.get_int("width", e.width);
-        declare("weight", {width_}, false, true);
+        // offset: the stored weight is a deviation from it (1 for weights kept around zero); the multiplier is
+        // offset + weight, formed in fp32
+        offset_ = (float)s.params.get_double("offset", 0.0);
+        // out: "float32" writes 32-bit rows whatever the activations' dtype (a norm that feeds a 32-bit residual stream)
+        const std::string out = s.params.get_string("out", "");
+        if (!out.empty() && out != "float32") throw ConfigError("rmsnorm: 'out' is \"float32\" or absent");
+        out_ = out.empty() ? e.dtype : DType::F32;
+        declare(s.params.get_string("weight_name", "weight"), {width_}, false, offset_ == 0.f);
+        name_ = s.params.get_string("weight_name", "weight");
     }
-    Tensor forward(Ops& ops, const Tensor& x) override { return ops.rmsnorm(x, tensor("weight"), eps_); }
+    Tensor forward(Ops& ops, const Tensor& x) override {
+        if (offset_ == 0.f && x.dtype == out_) return ops.rmsnorm(x, tensor(name_), eps_);
+        return ops.rmsnorm_to(x, tensor(name_), offset_, eps_, out_);
+    }
     bool as_rmsnorm(Tensor* weight, float* eps) const override {
-        *weight = tensor("weight");
+        if (offset_ != 0.f || out_ != env.dtype) return false;      // the products' fused norm knows plain weights only
+        *weight = tensor(name_);
         *eps = eps_;
         return true;
     }
 
 private:
-    float eps_;
+    float eps_, offset_;
     int64_t width_;
+    DType out_;
+    std::string name_;
 };
 
 // ------------------------------------------------------------------ rotary encoding, NeoX pairing
@@ -223,26 +250,44 @@ public:
         nq_ = (int)s.params.get_int("n_heads", 0);
         nkv_ = (int)s.params.get_int("n_kv_heads", nq_);
         hd_ = (int)s.params.get_int("head_dim", 0);
-        if (nq_ <= 0 || nkv_ <= 0 || hd_ <= 0) throw ConfigError("gqa_attention needs n_heads, n_kv_heads and head_dim");
+        vd_ = (int)s.params.get_int("v_head_dim", hd_);              // values may have a size of their own
+        if (nq_ <= 0 || nkv_ <= 0 || hd_ <= 0 || vd_ <= 0) throw ConfigError("gqa_attention needs n_heads, n_kv_heads and head_dim");
         if (nq_ % nkv_) throw ConfigError(format("%d heads cannot share %d key/value heads", nq_, nkv_));
         window_ = (int)s.params.get_int("window", 0);
+        keep_first_ = (int)s.params.get_int("keep_first", 0);         // behind a window, positions below this stay visible
+        if (keep_first_ < 0) throw ConfigError("gqa_attention: 'keep_first' must not be negative");
         scale_ = (float)s.params.get_double("scale", 1.0 / sqrt((double)hd_));
         qkv_bias_ = s.params.get_bool("qkv_bias", true);
         out_bias_ = s.params.get_bool("out_bias", false);
         position_ = adopt("", build<Position>("position", s.part("position"), e));
-        const int64_t qd = (int64_t)nq_ * hd_, kvd = (int64_t)nkv_ * hd_, w = e.width;
-        declare_stacked("w_qkv", qd + 2 * kvd, w);
-        if (qkv_bias_) declare_stacked("b_qkv", qd + 2 * kvd, 1);      // a vector: one column, members under one another
-        const char* names[3] = {"q_proj", "k_proj", "v_proj"};
-        const int64_t rows[3] = {qd, kvd, kvd}, first[3] = {0, qd, qd + kvd};
-        for (int i = 0; i < 3; ++i) {
-            declare(std::string(names[i]) + ".weight", {rows[i], w}).stack("w_qkv", first[i]);
-            if (qkv_bias_) declare(std::string(names[i]) + ".bias", {rows[i]}).stack("b_qkv", first[i]);
+        const int64_t qd = (int64_t)nq_ * hd_, kvd = (int64_t)nkv_ * hd_, vvd = (int64_t)nkv_ * vd_, w = e.width;
+        declare_stacked("w_qkv", qd + kvd + vvd, w);
+        if (qkv_bias_) declare_stacked("b_qkv", qd + kvd + vvd, 1);      // a vector: one column, members under one another
+        // tensor names: Hugging Face's unless the specification gives others ("names": {"q": ..., "k": ..., "v": ..., "o": ...})
+        const Json* names = s.params.find("names");
+        const char* roles[4] = {"q", "k", "v", "o"};
+        const char* defaults[4] = {"q_proj", "k_proj", "v_proj", "o_proj"};
+        std::string stem[4];
+        bool bare = false;
+        for (int i = 0; i < 4; ++i) {
+            stem[i] = defaults[i];
+            if (names && names->is_object() && names->has(roles[i])) {
+                stem[i] = names->at(roles[i]).as_string();
+                bare = true;
+            }
         }
-        declare("o_proj.weight", {w, qd});
-        if (out_bias_) declare("o_proj.bias", {w});
+        const std::string wsuf = bare ? "" : ".weight", bsuf = ".bias";
+        const int64_t rows[3] = {qd, kvd, vvd}, first[3] = {0, qd, qd + kvd};
+        for (int i = 0; i < 3; ++i) {
+            declare(stem[i] + wsuf, {rows[i], w}).stack("w_qkv", first[i]);
+            if (qkv_bias_) declare(stem[i] + bsuf, {rows[i]}).stack("b_qkv", first[i]);
+        }
+        o_name_ = stem[3] + wsuf;
+        o_bias_name_ = stem[3] + bsuf;
+        declare(o_name_, {w, (int64_t)nq_ * vd_});
+        if (out_bias_) declare(o_bias_name_, {w});
     }
-    CacheRequest cache_request() const override { return CacheRequest::kv(nkv_, hd_, window_); }
+    CacheRequest cache_request() const override { return CacheRequest::kv(nkv_, hd_, window_, vd_, keep_first_); }
 
     PartOut forward(Ops& ops, const Rows& h, const Tensor& residual, const StepContext& ctx, const CacheView& view,
                     Norm* then) override {
@@ -258,30 +303,35 @@ public:
         int rotary_dim = 0;
         Tensor qkv;
         if (position_->rotary(&denominators, &rotary_dim)) {
+            if (vd_ != hd_) throw ConfigError("gqa_attention: a rotary encoding with values of another size than the keys is not built");
             qkv = ops.qkv_rope_write(h, w_qkv, b_qkv, ctx.row_seq, ctx.row_pos, denominators, rotary_dim, nq_, nkv_, hd_, &view);
         } else {                                    // another encoding: it changes q and k itself
             qkv = ops.linear(h, w_qkv, b_qkv);
             position_->apply(ops, qkv, ctx, nq_, nkv_, hd_);
-            if (view.write) ops.rope_kv_write(qkv, ctx.row_seq, ctx.row_pos, nullptr, 0, nq_, nkv_, hd_, &view);
+            if (view.write) {
+                if (vd_ == hd_) ops.rope_kv_write(qkv, ctx.row_seq, ctx.row_pos, nullptr, 0, nq_, nkv_, hd_, &view);
+                else ops.kv_store(qkv, (int64_t)nq_ * hd_, (int64_t)(nq_ + nkv_) * hd_, view, ctx);
+            }
         }
-        Tensor mixed = ops.alloc(qkv.dtype, qkv.rows(), (int64_t)nq_ * hd_);
+        Tensor mixed = ops.alloc(qkv.dtype, qkv.rows(), (int64_t)nq_ * vd_);
         ops.attention(qkv, qkv.ld, mixed, view, ctx, nq_, nkv_, hd_, window_, scale_);
-        const Tensor& w_o = tensor("o_proj.weight");
-        const Tensor* b_o = out_bias_ ? &tensor("o_proj.bias") : nullptr;
+        const Tensor& w_o = tensor(o_name_);
+        const Tensor* b_o = out_bias_ ? &tensor(o_bias_name_) : nullptr;
         Tensor nw;
         float eps;
-        if (then && then->as_rmsnorm(&nw, &eps)) {
+        if (then && out_scale == 1.0f && residual.dtype == mixed.dtype && then->as_rmsnorm(&nw, &eps)) {
             auto r = ops.linear_norm(Rows(mixed), w_o, nw, eps, b_o, &residual);
             return PartOut(r.first, r.second);
         }
-        return PartOut(ops.linear(Rows(mixed), w_o, b_o, &residual));
+        return PartOut(ops.linear_residual(Rows(mixed), w_o, b_o, residual, out_scale));
     }
 
 private:
-    int nq_, nkv_, hd_, window_;
+    int nq_, nkv_, hd_, vd_, window_, keep_first_;
     float scale_;
     bool qkv_bias_, out_bias_;
     Position* position_;
+    std::string o_name_, o_bias_name_;
 };
 
 // ------------------------------------------------------------------ gated feed-forward: x + Wd (silu(Wg h) * (Wu h))
@@ -315,7 +365,7 @@ private:
 };
 
 // ------------------------------------------------------------------ pre-norm residual block
-// x = x + mixer(norm1(x)); x = x + feed_forward(norm2(x)).  The two sums happen inside the mixer's and the
+// x = x + mixer(norm1(x)); x = x + feed_forward(norm2(x)); x = token_input(x) (the last two if the block has them).  The sums happen inside the mixer's and the
 // feed-forward's last product (each gets the residual stream and returns it with its own output added), as in the
 // reference (transformer.cpp:997-1074).  Which mixer, feed-forward and norms a block has is its specification's.
 class PreNormBlock : public Block {
@@ -323,12 +373,19 @@ public:
     PreNormBlock(const PartSpec& s, const BuildEnv& e) : Block(e) {
         const PartSpec& n1 = s.part("norm1");
         const PartSpec& mx = s.part("mixer");
-        const PartSpec& n2 = s.part("norm2");
-        const PartSpec& ff = s.part("feed_forward");
         norm1_ = adopt(n1.prefix, build<Norm>("norm", n1, e));
         mixer_ = adopt(mx.prefix, build<Mixer>("mixer", mx, e));
-        norm2_ = adopt(n2.prefix, build<Norm>("norm", n2, e));
-        ffn_ = adopt(ff.prefix, build<FeedForward>("feed_forward", ff, e));
+        // a block may go without a feed-forward (then it has no second norm either), and may end with a token input
+        if (s.parts.count("feed_forward")) {
+            const PartSpec& n2 = s.part("norm2");
+            const PartSpec& ff = s.part("feed_forward");
+            norm2_ = adopt(n2.prefix, build<Norm>("norm", n2, e));
+            ffn_ = adopt(ff.prefix, build<FeedForward>("feed_forward", ff, e));
+        }
+        if (s.parts.count("token_input")) {
+            const PartSpec& ti = s.part("token_input");
+            token_input_ = adopt(ti.prefix, build<TokenInput>("token_input", ti, e));
+        }
     }
     CacheRequest cache_request() const override { return mixer_->cache_request(); }
     Norm* first_norm() override { return norm1_; }
@@ -336,9 +393,17 @@ public:
     PartOut forward(Ops& ops, const Tensor& x, const Rows* normed, const StepContext& ctx, const CacheView& view,
                     Norm* then) override {
         Rows h = normed ? *normed : Rows(norm1_->forward(ops, x));
-        PartOut a = mixer_->forward(ops, h, x, ctx, view, norm2_);
-        Rows h2 = a.has_normed ? a.normed : Rows(norm2_->forward(ops, a.x));
-        PartOut b = ffn_->forward(ops, h2, a.x, ctx, then);
+        Norm* after_last = token_input_ ? nullptr : then;       // a token input changes the stream after the last product
+        PartOut b = mixer_->forward(ops, h, x, ctx, view, ffn_ ? norm2_ : after_last);
+        if (ffn_) {
+            Rows h2 = b.has_normed ? b.normed : Rows(norm2_->forward(ops, b.x));
+            const Tensor mixed = b.x;
+            b = ffn_->forward(ops, h2, mixed, ctx, after_last);
+        }
+        if (token_input_) {
+            token_input_->forward(ops, b.x, ctx);
+            b.has_normed = false;
+        }
         if (then && !b.has_normed) {
             b.normed = Rows(then->forward(ops, b.x));
             b.has_normed = true;
@@ -347,9 +412,10 @@ public:
     }
 
 private:
-    Norm *norm1_, *norm2_;
-    Mixer* mixer_;
-    FeedForward* ffn_;
+    Norm *norm1_ = nullptr, *norm2_ = nullptr;
+    Mixer* mixer_ = nullptr;
+    FeedForward* ffn_ = nullptr;
+    TokenInput* token_input_ = nullptr;
 };
 
 namespace {

@@ -49,6 +49,8 @@ public:
         : seed_(seed), dtype_(dtype), on_device_(on_device) {
         for (const auto& e : expected)
             if (!decl_.count(e.name)) {
+                for (int64_t d : e.decl.shape)
+                    if (d < 0) throw WeightsError("tensor '" + e.name + "' has a size that only a checkpoint gives; the configuration must name it to draw random weights");
                 decl_[e.name] = e.decl;
                 order_.push_back(e.name);
             }
@@ -151,7 +153,10 @@ void write_random_model(const std::string& dir, const Json& config_json, uint64_
         t.name = e.name;
         t.shape = e.decl.shape;
         int64_t n = 1;
-        for (int64_t s : t.shape) n *= s;
+        for (int64_t s : t.shape) {
+            if (s < 0) throw WeightsError("tensor '" + e.name + "' has a size that only a checkpoint gives; the configuration must name it to draw random weights");
+            n *= s;
+        }
         if (e.decl.integer) {
             t.dtype = "I32";
             t.bytes.assign((size_t)n * 4, 0);

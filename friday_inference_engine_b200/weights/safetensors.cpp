@@ -212,8 +212,12 @@ void check_names(const std::vector<Part::Named>& expected, const WeightSource& s
         } else if (!source.info(e.name, &t)) {
             err.missing.push_back(e.name);
             notes.push_back(e.name);
-        } else if (t.shape != e.decl.shape) {
-            err.wrong_shape.push_back(ShapeMismatch{e.name, t.shape, e.decl.shape});
+        } else {
+            // -1 in a declared shape: that size is the checkpoint's to give
+            bool same = t.shape.size() == e.decl.shape.size();
+            for (size_t i = 0; same && i < t.shape.size(); ++i)
+                same = e.decl.shape[i] < 0 ? t.shape[i] > 0 : t.shape[i] == e.decl.shape[i];
+            if (!same) err.wrong_shape.push_back(ShapeMismatch{e.name, t.shape, e.decl.shape});
         }
     }
     for (const auto& n : have)

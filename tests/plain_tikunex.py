@@ -159,12 +159,17 @@ def gated_linear_attention(h, t, p, m, eps):
 # ---------------------------------------------------------------------------
 # feed-forward and the per-layer token input
 # ---------------------------------------------------------------------------
-def routed_experts(h, t, p, m):
+def routed_experts(h, t, p, m, gaps=None):
+    """gaps, if given, is an array [T] that keeps, per token, the smallest distance seen so far between the last
+    chosen logit and the first one that was not chosen (how close the choice was)."""
     E, top = m["router"]["experts"], m["router"]["top"]
     z = h @ t[p + "router"].T + t[p + "router.b"]
     out = np.zeros((h.shape[0], t[p + "e0.down"].shape[0]), dtype=F64)
     for i in range(h.shape[0]):
         chosen = np.argsort(-z[i], kind="stable")[:top]
+        if gaps is not None and top < E:
+            ordered = np.sort(z[i])[::-1]
+            gaps[i] = min(gaps[i], ordered[top - 1] - ordered[top])
         w = np.exp(z[i, chosen] - z[i, chosen].max())
         w = w / w.sum()
         for e, we in zip(chosen, w):
@@ -198,7 +203,7 @@ def run_order(cfg):
     return order
 
 
-def layer_forward(cfg, t, i, X, tokens):
+def layer_forward(cfg, t, i, X, tokens, gaps=None):
     L = cfg["layers"][i]
     eps = cfg["norm"]["eps"]
     p = "l%d." % i
@@ -210,14 +215,14 @@ def layer_forward(cfg, t, i, X, tokens):
     else:
         raise ValueError("mixer type %r" % L["type"])
     if L.get("mlp"):
-        X = X + routed_experts(unit_offset_norm(X, t[p + "norm2"], eps), t, p + "mlp.", L["mlp"])
+        X = X + routed_experts(unit_offset_norm(X, t[p + "norm2"], eps), t, p + "mlp.", L["mlp"], gaps)
     side = cfg.get("token_side")
     if side:
         X = X + token_side(X, tokens, i, t, p + "side.", side["dim"], eps)
     return X
 
 
-def forward(cfg, t, tokens, keep_layers=False):
+def forward(cfg, t, tokens, keep_layers=False, gaps=None):
     """logits [T, vocab]; with keep_layers also the residual stream after every layer run."""
     eps = cfg["norm"]["eps"]
     x0 = unit_offset_norm(t["embed"][np.asarray(tokens)], t["embed.norm"], eps)
@@ -226,7 +231,15 @@ def forward(cfg, t, tokens, keep_layers=False):
     for i, first in run_order(cfg):
         if first:
             X = np.concatenate([X, x0], axis=1) @ t["loop.in"].T
-        X = layer_forward(cfg, t, i, X, tokens)
+        X = layer_forward(cfg, t, i, X, tokens, gaps)
         after.append(X)
     logits = unit_offset_norm(X, t["final.norm"], eps) @ t["head"].T
     return (logits, np.stack(after)) if keep_layers else logits
+
+
+def greedy(cfg, t, prompt, n_new):
+    """The tokens that greedy decoding appends to `prompt` (the first maximum wins)."""
+    tokens = list(prompt)
+    for _ in range(n_new):
+        tokens.append(int(np.argmax(forward(cfg, t, tokens)[-1])))
+    return tokens[len(prompt):]

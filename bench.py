@@ -543,6 +543,120 @@ def sweeps(Engine, args):
     return 0
 
 
+def tikunex_config(width, layers=4, vocab=32768, window=1024, experts=8, top=2):
+    """A Tikunex configuration whose layers have sizes like a real model's of this width: gated linear attention with
+    keys of half and values of the full width; windowed attention (keys of 64, values of 128) beside shift-decay mixing
+    with heads of 64; `experts` experts of inner size `width`, `top` chosen; the last three layers run twice."""
+    gla = {"heads": width // 128, "dim": 64, "vdim": 128, "tau": 16.0, "decay_rank": 64}
+    par = {"left": {"heads": width // 128, "kv_heads": max(1, width // 512), "dim": 64, "vdim": 128, "scale": 0.125,
+                    "mask": {"size": window, "keep_first": 4}},
+           "right": {"heads": width // 64, "dim": 64, "decay_rank": 64}, "left_scale": 1.0, "right_scale": 1.0}
+    mlp = {"kind": "moe", "expert": {"ff": width}, "router": {"experts": experts, "top": top}}
+    ls = [{"type": "gla" if i % 2 == 0 else "parallel", "mixer": gla if i % 2 == 0 else par, "mlp": mlp} for i in range(layers)]
+    return {"architecture": "Tikunex", "vocab": vocab, "width": width, "norm": {"eps": 1e-5}, "layers": ls,
+            "loop": {"start": 1, "stop": layers, "times": 2}, "token_side": {"dim": 64}}
+
+
+def tikunex_numbers(cfg, batch, context):
+    """What a decode step of `batch` sequences must read and what a prompt token costs, per run of the layers."""
+    w, v = cfg["width"], cfg["vocab"]
+    loop = cfg.get("loop") or {"start": 0, "stop": 0, "times": 1}
+    runs = [1 + (loop["times"] - 1) * (loop["start"] <= i < loop["stop"]) for i in range(len(cfg["layers"]))]
+    weight_bytes = state_bytes = kv_bytes = 0
+    flops = 0                                          # per prompt token
+    passes = loop["times"] if cfg.get("loop") else 0
+    weight_bytes += 2 * (passes > 0) * 2 * w * w + 2 * v * w
+    flops += 2 * passes * 2 * w * w + 2 * v * w
+    for L, n in zip(cfg["layers"], runs):
+        m = L["mixer"]
+        if L["type"] == "gla":
+            hk, hv, r = m["heads"] * m["dim"], m["heads"] * m["vdim"], m["decay_rank"]
+            mat = (2 * hk + 2 * hv) * w + r * w + hk * r + w * hv
+            st = m["heads"] * m["dim"] * m["vdim"]
+            scan = 4 * st
+            att = 0
+        else:
+            l, rt = m["left"], m["right"]
+            qd, kd, vd = l["heads"] * l["dim"], l["kv_heads"] * l["dim"], l["kv_heads"] * l["vdim"]
+            hd = rt["heads"] * rt["dim"]
+            mat = (qd + kd + vd) * w + w * l["heads"] * l["vdim"] + 4 * hd * w + rt["decay_rank"] * (w + hd) + w * hd
+            st = rt["heads"] * rt["dim"] * rt["dim"] + w
+            scan = 4 * rt["heads"] * rt["dim"] * rt["dim"]
+            seen = min(context, l["mask"]["size"] + l["mask"]["keep_first"])
+            kv_bytes += n * batch * seen * (kd + vd) * 2
+            att = 2 * l["heads"] * (l["dim"] + l["vdim"]) * seen // 2
+        ff = 0
+        if L.get("mlp"):
+            e, top, f = L["mlp"]["router"]["experts"], L["mlp"]["router"]["top"], L["mlp"]["expert"]["ff"]
+            distinct = e * (1.0 - (1.0 - top / e) ** batch)
+            weight_bytes += 2 * (e * w + distinct * 3 * f * w)
+            ff = e * w + top * 3 * f * w
+        side = 2 * cfg["token_side"]["dim"] * w if cfg.get("token_side") else 0
+        weight_bytes += 2 * (mat + side)              # a layer's weights are read again in every pass of the loop
+        weight_bytes += (n - 1) * 2 * (mat + side)
+        if L.get("mlp") and n > 1:
+            weight_bytes += (n - 1) * 2 * (e * w + distinct * 3 * f * w)
+        state_bytes += n * batch * st * 4 * 2
+        flops += n * (2 * (mat + ff + side) + scan + att)
+    return {"step_bytes": weight_bytes + state_bytes + kv_bytes, "flops_per_token": flops}
+
+
+def design_compare(Engine, args):
+    """Tikunex beside the Qwen2.5 dense decoder at equal width and depth (random weights): one prompt and decode steps,
+    with the share of each kind of kernel in the prompt (event-bracketed).  One line of text per measurement."""
+    pk = peaks()
+    prompt_len, batch, context = 2048, args.batch, 1024
+    for width in [int(v) for v in args.design_compare.split(",") if v]:
+        layers = args.layers or 4
+        designs = [
+            ("tikunex", tikunex_config(width, layers)),
+            ("qwen2", dict(QWEN25_7B, num_hidden_layers=2 * layers - 1, hidden_size=width, num_attention_heads=width // 128,
+                           num_key_value_heads=max(1, width // 512), intermediate_size=3 * width, vocab_size=32768)),
+        ]
+        for name, cfg in designs:
+            eng = Engine(config=cfg, seed=0, dtype="bfloat16", max_ctx=4096, max_batch=batch, max_tokens=batch * 4096 + 8192)
+            if name == "tikunex":
+                nums = tikunex_numbers(cfg, batch, context + 64)
+                flops_tok, step_bytes = nums["flops_per_token"], nums["step_bytes"]
+            else:
+                q = model_numbers(cfg, cfg["num_hidden_layers"])
+                flops_tok = 2 * (q["matmul_params"] + q["head_params"]) + 2 * cfg["num_hidden_layers"] * width * prompt_len
+                step_bytes = q["step_weight_bytes"] + q["kv_bytes_per_token"] * (context + 64) * batch
+            ms = time_prefill(eng, prompt_len, 2, 5)
+            print("%-8s width %5d: prompt of %d tokens %8.2f ms, %9.0f tok/s, %.3f of the %s bf16 peak" % (
+                name, width, prompt_len, ms, prompt_len * 1000.0 / ms, flops_tok * prompt_len / (ms * 1e-3) / 1e12 / pk["bf16_tflops"],
+                pk["source"]), flush=True)
+            prompts = random_prompts(batch, context, eng.vocab_size, 3)
+            dms, launches, _, _ = time_decode(eng, prompts, min(args.steps, 32), args.warmup)
+            print("%-8s width %5d: decode, %d sequences of %d tokens %7.3f ms per step, %8.1f tok/s, %.3f of the %s HBM roofline, %d launches per step" % (
+                name, width, batch, context, dms, batch * 1000.0 / dms, step_bytes / (dms * 1e-3) / 1e9 / pk["hbm_gbs"], pk["source"],
+                launches // min(args.steps, 32)), flush=True)
+            eng.check()
+            del eng
+            prof = Engine(config=cfg, seed=0, dtype="bfloat16", max_ctx=4096, max_batch=2, max_tokens=16384, profile=True)
+            (p,) = random_prompts(1, prompt_len, prof.vocab_size, 5)
+            for _ in range(3):
+                s = prof.alloc_slot()
+                prof.step([s], [p], [[prompt_len - 1]])
+                prof.free_slot(s)
+                pr = prof.profile()
+            print("%-8s width %5d: the prompt's kernels: products %.2f ms (%d), attention and scans %.2f ms (%d), others %.2f ms (%d)" % (
+                name, width, pr["product_ms"], pr["product_calls"], pr["attention_ms"], pr["attention_calls"], pr["other_ms"],
+                pr["other_calls"]), flush=True)
+            s = prof.alloc_slot()
+            prof.step([s], [p[:context]], [[]])
+            prof.profile()
+            for tok in p[context:context + 8]:
+                prof.step([s], [[tok]], [[0]])
+            pr = prof.profile()
+            print("%-8s width %5d: one-token steps' kernels (1 sequence of %d tokens, per step): products %.3f ms (%d), attention and scans %.3f ms (%d), others %.3f ms (%d)" % (
+                name, width, context, pr["product_ms"] / 8, pr["product_calls"] // 8, pr["attention_ms"] / 8, pr["attention_calls"] // 8,
+                pr["other_ms"] / 8, pr["other_calls"] // 8), flush=True)
+            prof.free_slot(s)
+            del prof
+    return 0
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -564,6 +678,9 @@ def main():
                     help="one prompt of each of these lengths, e.g. 2048,8192,32000: one line each")
     ap.add_argument("--prefill-chunk", type=int, default=0, dest="prefill_chunk",
                     help="most tokens of a sequence per pass in the sweeps (0: the engine's own)")
+    ap.add_argument("--design-compare", default="", dest="design_compare",
+                    help="widths, e.g. 1024,2048,4096: a Tikunex model with layers of that size beside the Qwen2.5 decoder of "
+                         "equal width (prompt, decode steps, kernel shares): lines of text")
     ap.add_argument("--timeline", action="store_true",
                     help="print the kernels of one decode step as they run inside the captured graph (torch profiler)")
     args = ap.parse_args()
@@ -579,6 +696,8 @@ def main():
 
     from friday_inference_engine_b200 import Engine
 
+    if args.design_compare:
+        return design_compare(Engine, args)
     if args.decode_sweep or args.prompt_sweep:
         return sweeps(Engine, args)
     cfg = dict(SHAPES[args.model_size])

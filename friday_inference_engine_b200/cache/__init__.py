@@ -13,8 +13,16 @@ from ..native import CacheError, CacheFull  # noqa: F401
 PAGE = 64
 
 
-def kv_request(n_kv_heads, head_dim, window=None):
-    return {"kind": "kv", "n_kv_heads": int(n_kv_heads), "head_dim": int(head_dim), "window": int(window or 0)}
+def kv_request(n_kv_heads, head_dim, window=None, v_head_dim=None, keep_first=0):
+    """v_head_dim: size of a value head if it differs from the keys'; keep_first: behind a window, positions below this
+    stay visible, so their pages are held as long as the sequence lives."""
+    return {"kind": "kv", "n_kv_heads": int(n_kv_heads), "head_dim": int(head_dim), "window": int(window or 0),
+            "v_head_dim": int(v_head_dim or 0), "keep_first": int(keep_first)}
+
+
+def several(*parts):
+    """What a mixer asks for that runs others side by side: one request per member."""
+    return {"kind": "several", "parts": list(parts)}
 
 
 def state_request(shape, dtype="float32"):

@@ -78,11 +78,18 @@ Json ints_json(const std::vector<int>& v) {
 
 Json request_json(const CacheRequest& r) {
     Json j = Json::object();
-    j.set("kind", Json(r.kind == CacheRequest::KV ? "kv" : r.kind == CacheRequest::State ? "state" : "none"));
+    j.set("kind", Json(r.kind == CacheRequest::KV ? "kv" : r.kind == CacheRequest::State ? "state"
+                       : r.kind == CacheRequest::Several ? "several" : "none"));
     if (r.kind == CacheRequest::KV) {
         j.set("n_kv_heads", Json(r.n_kv_heads));
         j.set("head_dim", Json(r.head_dim));
         j.set("window", Json(r.window));
+        j.set("v_head_dim", Json(r.value_dim()));
+        j.set("keep_first", Json(r.keep_first));
+    } else if (r.kind == CacheRequest::Several) {
+        Json parts = Json::array();
+        for (const auto& p : r.parts) parts.push(request_json(p));
+        j.set("parts", parts);
     } else if (r.kind == CacheRequest::State) {
         j.set("shape", ints_json(r.state_shape));
         j.set("dtype", Json(dtype_name(r.state_dtype)));
@@ -92,7 +99,15 @@ Json request_json(const CacheRequest& r) {
 
 CacheRequest request_from(const Json& j) {
     const std::string kind = j.get_string("kind", "none");
-    if (kind == "kv") return CacheRequest::kv((int)j.get_int("n_kv_heads", 0), (int)j.get_int("head_dim", 0), (int)j.get_int("window", 0));
+    if (kind == "kv")
+        return CacheRequest::kv((int)j.get_int("n_kv_heads", 0), (int)j.get_int("head_dim", 0), (int)j.get_int("window", 0),
+                                (int)j.get_int("v_head_dim", 0), (int)j.get_int("keep_first", 0));
+    if (kind == "several") {
+        std::vector<CacheRequest> parts;
+        if (const Json* ps = j.find("parts"))
+            for (const Json& p : ps->items()) parts.push_back(request_from(p));
+        return CacheRequest::several(parts);
+    }
     if (kind == "state") {
         std::vector<int64_t> shape;
         if (const Json* s = j.find("shape"))
@@ -237,6 +252,7 @@ FR_API int friday_describe_model(const char* config_json, const char** json) {
             e.set("layer", Json(c.layer));
             e.set("cache", Json(c.cache));
             e.set("write", Json(c.write));
+            e.set("inject", Json(c.inject));
             program.push(e);
         }
         out.set("program", program);
@@ -410,6 +426,9 @@ static Json cache_json(const Cache& c) {
         j.set("pages_free", Json(g->pages.free_count()));
         j.set("pool_shape", ints_json(std::vector<int64_t>{(int64_t)g->entries.size(), g->n_pages, PAGE, g->request.n_kv_heads,
                                                             g->request.head_dim}));
+        j.set("value_pool_shape", ints_json(std::vector<int64_t>{(int64_t)g->entries.size(), g->n_pages, PAGE,
+                                                                  g->request.n_kv_heads, g->request.value_dim()}));
+        j.set("keep_first", Json(g->request.keep_first));
         Json table = Json::array();
         for (int s = 0; s < c.max_slots; ++s) table.push(ints_json(std::vector<int>(g->table_row(s), g->table_row(s) + g->width)));
         j.set("table", table);

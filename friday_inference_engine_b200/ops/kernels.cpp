@@ -98,6 +98,8 @@ FAMILY(GemmSimt, gemm_simt, "gemm_simt", resolve(h, fam, "gemm_simt", t.gemm);)
 FAMILY(GemmTc, gemm_tc, "gemm_tc", resolve(h, fam, "gemm_tc_fused", t.fused); resolve(h, fam, "gemm_tc_plan", t.plan);)
 FAMILY(AttentionSimt, attention_simt, "attention_simt", resolve(h, fam, "attention_simt", t.run);
        resolve(h, fam, "attention_simt_masked", t.masked);)
+FAMILY(AttentionWindow, attention_window, "attention_window", resolve(h, fam, "attention_window_fits", t.fits);
+       resolve(h, fam, "attention_window", t.run);)
 FAMILY(Residual, residual, "residual", resolve(h, fam, "residual_norm_cast", t.norm_cast);
        resolve(h, fam, "residual_concat_cast", t.concat_cast); resolve(h, fam, "residual_add_scaled", t.add_scaled);
        resolve(h, fam, "residual_kv_store", t.kv_store); resolve(h, fam, "residual_token_input", t.token_input);)

@@ -48,6 +48,12 @@ struct AttentionSimt {
     int (*masked)(const void*, int, void*, const void*, const void*, const int*, int, int, const int*, const int*, int, int, int,
                   int, int, int, int, float, float, int, float*, int, cudaStream_t);
 };
+struct AttentionWindow {
+    last_error_fn last_error;
+    int (*fits)(int, int, int);
+    int (*run)(const void*, int, void*, const void*, const void*, const int*, int, int, const int*, const int*, const int*, int, int,
+               int, int, int, int, int, int, float, float, cudaStream_t);
+};
 struct Residual {
     last_error_fn last_error;
     int (*norm_cast)(const void*, int, const void*, int, float, void*, int, int, int, float, cudaStream_t);
@@ -102,6 +108,7 @@ const AttentionSimt& attention_simt();
 const AttentionMma& attention_mma();
 const AttentionTc& attention_tc();
 const Sampling& sampling();
+const AttentionWindow& attention_window();
 const Residual& residual();
 const Recurrence& recurrence();
 const Routed& routed();

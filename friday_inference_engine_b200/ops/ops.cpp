@@ -662,6 +662,18 @@ void Ops::attention(const Tensor& q, int64_t q_stride, Tensor& out, const CacheV
     const int vd = view.v_head_dim > 0 ? view.v_head_dim : head_dim;
     const int keep = window > 0 ? view.keep_first : 0;
     if (vd != head_dim || keep > 0 || out_scale != 1.0f) {
+        // prompts in bf16: tensor cores (mma.sync), 32-bit softmax; FRIDAY_ATTN_WINDOW=0 keeps them on the CUDA cores
+        if (out.dtype == DType::BF16 && !ctx.decode && ctx.seq_start != nullptr && env_on("FRIDAY_ATTN_WINDOW") &&
+            head_dim <= 128 && vd <= 128 && view.page_size == 64) {
+            const auto& k = kernels::attention_window();
+            Timed t(*this, Attention);
+            call(launches_, k,
+                 k.run(q.data, (int)q_stride, out.data, view.k_pool, view.v_pool, view.block_table, view.table_width, view.page_size,
+                       ctx.seq_start, ctx.seq_qlen, ctx.seq_pos0, ctx.n_seqs, ctx.max_q_len, n_heads, n_kv_heads, head_dim, vd, window,
+                       keep, scale, out_scale, stream_),
+                 "attention_window");
+            return;
+        }
         // the general form: CUDA cores, fp32 arithmetic
         const int rows_ = (int)out.rows();
         int kv_reach = ctx.max_kv_len;

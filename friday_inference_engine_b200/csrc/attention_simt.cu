@@ -78,26 +78,55 @@ __global__ void __launch_bounds__(128) attention_kernel(AttnArgs p) {
             qv[i] = d < p.hd ? fr_load(q + d) * p.scale : 0.f;
         }
         const int* table = p.block_table + (size_t)seq * p.table_width;
-        for (int i = i0; i < i1; ++i) {
-            const int j = i < kept ? i : lo + (i - kept);
-            const size_t at = ((size_t)table[j / p.page] * p.page + j % p.page) * p.nkv + kvh;
-            const T* kr = (const T*)p.k_pool + at * p.hd;
-            const T* vr = (const T*)p.v_pool + at * p.vd;
-            float s = 0.f;
+        // four keys at a time: their loads are issued together, so that a warp waits for memory once per four keys
+        for (int i = i0; i < i1; i += 4) {
+            const T* kr[4];
+            const T* vr[4];
+            float s4[4];
 #pragma unroll
-            for (int c = 0; c < MAX_PER_LANE; ++c) {
-                const int d = lane + 32 * c;
-                if (d < p.hd) s = fmaf(qv[c], fr_load(kr + d), s);
+            for (int u = 0; u < 4; ++u) {
+                const int iu = min(i + u, i1 - 1);           // past the end: the last key again (its weight is set to zero)
+                const int j = iu < kept ? iu : lo + (iu - kept);
+                const size_t at = ((size_t)table[j / p.page] * p.page + j % p.page) * p.nkv + kvh;
+                kr[u] = (const T*)p.k_pool + at * p.hd;
+                vr[u] = (const T*)p.v_pool + at * p.vd;
             }
-            s = fr_warp_sum(s);
-            const float m_new = fmaxf(m, s);
-            const float alpha = expf(m - m_new);      // exp(-inf) = 0 on the first key
-            const float e = expf(s - m_new);
-            l = l * alpha + e;
+#pragma unroll
+            for (int u = 0; u < 4; ++u) {
+                float s = 0.f;
+#pragma unroll
+                for (int c = 0; c < MAX_PER_LANE; ++c) {
+                    const int d = lane + 32 * c;
+                    if (d < p.hd) s = fmaf(qv[c], fr_load(kr[u] + d), s);
+                }
+                s4[u] = s;
+            }
+            float vv[4][MAX_PER_LANE];
+#pragma unroll
+            for (int u = 0; u < 4; ++u)
+#pragma unroll
+                for (int c = 0; c < MAX_PER_LANE; ++c) {
+                    const int d = lane + 32 * c;
+                    vv[u][c] = d < p.vd ? fr_load(vr[u] + d) : 0.f;
+                }
+#pragma unroll
+            for (int o = 16; o > 0; o >>= 1)
+#pragma unroll
+                for (int u = 0; u < 4; ++u) s4[u] += __shfl_xor_sync(0xffffffffu, s4[u], o);
+            float m_new = m;
+#pragma unroll
+            for (int u = 0; u < 4; ++u)
+                if (i + u < i1) m_new = fmaxf(m_new, s4[u]);
+            const float alpha = expf(m - m_new);      // exp(-inf) = 0 on the first keys
+            float e4[4];
+#pragma unroll
+            for (int u = 0; u < 4; ++u) e4[u] = i + u < i1 ? expf(s4[u] - m_new) : 0.f;
+            l = l * alpha + ((e4[0] + e4[1]) + (e4[2] + e4[3]));
 #pragma unroll
             for (int c = 0; c < MAX_PER_LANE; ++c) {
                 const int d = lane + 32 * c;
-                if (d < p.vd) acc[c] = acc[c] * alpha + e * fr_load(vr + d);
+                if (d < p.vd)
+                    acc[c] = acc[c] * alpha + ((e4[0] * vv[0][c] + e4[1] * vv[1][c]) + (e4[2] * vv[2][c] + e4[3] * vv[3][c]));
             }
             m = m_new;
         }

@@ -11,6 +11,8 @@
 
 FR_EXPORT const char* residual_last_error() { return fr_error_text; }
 
+typedef __nv_bfloat16 bf16;
+
 namespace {
 
 __device__ __forceinline__ float block_sum(float v, float* partial) {
@@ -92,15 +94,51 @@ __device__ __forceinline__ float gelu_tanh(float z) {
     return 0.5f * z * (1.0f + tanhf(0.7978845608028654f * (z + 0.044715f * z * z * z)));
 }
 
-// The per-layer token input, one block per row, in place on the 32-bit residual stream:
+// The per-layer token input, in place on the 32-bit residual stream:
 //   e = table[token][col0 .. col0 + dim);  g = gelu_tanh(gate x) * e;  y = proj g;
 //   x += y / sqrt(mean(y^2) + eps) * norm
-// gate [dim][width], proj [width][dim], norm [width], table [vocab][table_ld] in the dtype TW.
+// gate [dim][width], proj [width][dim], norm [width], table [vocab][table_ld] in the dtype TW.  Two kernels: a warp per
+// (row, channel of g), then a block per row for the projection, its norm and the sum.
 template <typename TW>
-__global__ void __launch_bounds__(256)
-token_input_kernel(float* __restrict__ x, const int* __restrict__ tokens, const int* __restrict__ row_seq,
-                   const TW* __restrict__ table, int table_ld, int col0, int vocab, const TW* __restrict__ gate,
-                   const TW* __restrict__ proj, FrVec norm, int width, int dim, float eps) {
+__global__ void __launch_bounds__(128)
+token_gate_kernel(const float* __restrict__ x, const int* __restrict__ tokens, const int* __restrict__ row_seq,
+                  const TW* __restrict__ table, int table_ld, int col0, int vocab, const TW* __restrict__ gate,
+                  float* __restrict__ g, int rows, int width, int dim) {
+    fr_pdl_wait();
+    fr_pdl_launch();
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int item = blockIdx.x * 4 + warp;
+    if (item >= rows * dim) return;
+    const int row = item / dim, d = item - row * dim;
+    const int token = tokens[row];
+    if ((row_seq != nullptr && row_seq[row] < 0) || token < 0 || token >= vocab) return;
+    const float* xr = x + (size_t)row * width;
+    const TW* gr = gate + (size_t)d * width;
+    float s = 0.f;
+    constexpr int PER = 16 / sizeof(TW);
+    if (width % PER == 0 && ((((uintptr_t)xr) | ((uintptr_t)gr)) & 15) == 0) {
+        for (int c = lane * PER; c < width; c += 32 * PER) {
+            const uint4 wv = *(const uint4*)(gr + c);
+#pragma unroll
+            for (int i = 0; i < PER; i += 4) {
+                const float4 xv = *(const float4*)(xr + c + i);
+                s = fmaf(xv.x, fr_load((const TW*)&wv + i), s);
+                s = fmaf(xv.y, fr_load((const TW*)&wv + i + 1), s);
+                s = fmaf(xv.z, fr_load((const TW*)&wv + i + 2), s);
+                s = fmaf(xv.w, fr_load((const TW*)&wv + i + 3), s);
+            }
+        }
+    } else {
+        for (int c = lane; c < width; c += 32) s = fmaf(xr[c], fr_load(gr + c), s);
+    }
+    s = fr_warp_sum(s);
+    if (lane == 0) g[(size_t)row * dim + d] = gelu_tanh(s) * fr_load(table + (size_t)token * table_ld + col0 + d);
+}
+
+template <typename TW>
+__global__ void __launch_bounds__(1024)
+token_proj_kernel(float* __restrict__ x, const int* __restrict__ tokens, const int* __restrict__ row_seq, int vocab,
+                  const float* __restrict__ gs, const TW* __restrict__ proj, FrVec norm, int width, int dim, float eps) {
     extern __shared__ float sm[];
     float* g = sm;                // [dim]
     float* y = sm + dim;          // [width]
@@ -111,26 +149,57 @@ token_input_kernel(float* __restrict__ x, const int* __restrict__ tokens, const 
     const int token = tokens[row];
     if ((row_seq != nullptr && row_seq[row] < 0) || token < 0 || token >= vocab) return;
     float* xr = x + (size_t)row * width;
-    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, warps = blockDim.x >> 5;
-    for (int d = warp; d < dim; d += warps) {
-        const TW* gr = gate + (size_t)d * width;
-        float s = 0.f;
-        for (int c = lane; c < width; c += 32) s = fmaf(xr[c], fr_load(gr + c), s);
-        s = fr_warp_sum(s);
-        if (lane == 0) g[d] = gelu_tanh(s) * fr_load(table + (size_t)token * table_ld + col0 + d);
-    }
+    for (int d = threadIdx.x; d < dim; d += blockDim.x) g[d] = gs[(size_t)row * dim + d];
     __syncthreads();
     float ss = 0.f;
     for (int c = threadIdx.x; c < width; c += blockDim.x) {
         const TW* pr = proj + (size_t)c * dim;
         float s = 0.f;
-        for (int d = 0; d < dim; ++d) s = fmaf(g[d], fr_load(pr + d), s);
+        constexpr int PER = 16 / sizeof(TW);
+        if (dim % PER == 0 && (((uintptr_t)pr) & 15) == 0) {
+            for (int d = 0; d < dim; d += PER) {
+                const uint4 pv = *(const uint4*)(pr + d);
+#pragma unroll
+                for (int i = 0; i < PER; ++i) s = fmaf(g[d + i], fr_load((const TW*)&pv + i), s);
+            }
+        } else {
+            for (int d = 0; d < dim; ++d) s = fmaf(g[d], fr_load(pr + d), s);
+        }
         y[c] = s;
         ss = fmaf(s, s, ss);
     }
     ss = block_sum(ss, partial);
     const float inv = 1.0f / sqrtf(ss / (float)width + eps);
     for (int c = threadIdx.x; c < width; c += blockDim.x) xr[c] += y[c] * inv * norm.at(c);
+}
+
+// Many rows: the two projections run as products; these are the steps between them.
+// g[row][d] = gelu_tanh(z[row][d]) * table[token][col0 + d], in the dtype of g
+template <typename TW>
+__global__ void gelu_table_kernel(const float* __restrict__ z, const int* __restrict__ tokens, const TW* __restrict__ table,
+                                  int table_ld, int col0, int vocab, TW* __restrict__ g, int rows, int dim) {
+    fr_pdl_wait();
+    fr_pdl_launch();
+    for (int idx = blockIdx.x * blockDim.x + threadIdx.x; idx < rows * dim; idx += gridDim.x * blockDim.x) {
+        const int row = idx / dim, d = idx - row * dim;
+        const int token = tokens[row];
+        const float e = token >= 0 && token < vocab ? fr_load(table + (size_t)token * table_ld + col0 + d) : 0.f;
+        fr_store(g + idx, gelu_tanh(z[idx]) * e);
+    }
+}
+
+// x += y / sqrt(mean(y^2) + eps) * norm, one block per row
+__global__ void __launch_bounds__(256) rms_add_kernel(float* __restrict__ x, const float* __restrict__ y, FrVec norm, int width, float eps) {
+    __shared__ float partial[32];
+    fr_pdl_wait();
+    fr_pdl_launch();
+    float* xr = x + (size_t)blockIdx.x * width;
+    const float* yr = y + (size_t)blockIdx.x * width;
+    float ss = 0.f;
+    for (int c = threadIdx.x; c < width; c += blockDim.x) ss = fmaf(yr[c], yr[c], ss);
+    ss = block_sum(ss, partial);
+    const float inv = 1.0f / sqrtf(ss / (float)width + eps);
+    for (int c = threadIdx.x; c < width; c += blockDim.x) xr[c] += yr[c] * inv * norm.at(c);
 }
 
 inline int blocks_for(long long n) {
@@ -140,8 +209,6 @@ inline int blocks_for(long long n) {
 }
 
 }  // namespace
-
-typedef __nv_bfloat16 bf16;
 
 FR_EXPORT int residual_norm_cast(const void* x, int in_dtype, const void* w, int w_dtype, float offset, void* y, int out_dtype,
                                  int n_rows, int width, float eps, cudaStream_t stream) {
@@ -207,24 +274,50 @@ FR_EXPORT int residual_kv_store(const void* src, int ld, int k_off, int v_off, i
     return FR_OK;
 }
 
+// g_scratch: [n_rows][dim] floats
 FR_EXPORT int residual_token_input(float* x, const int* tokens, const int* row_seq, const void* table, int table_ld, int col0,
                                    int vocab, const void* gate, const void* proj, const void* norm, int norm_dtype, int n_rows,
-                                   int width, int dim, float eps, int w_dtype, cudaStream_t stream) {
+                                   int width, int dim, float eps, float* g_scratch, int w_dtype, cudaStream_t stream) {
     if (n_rows <= 0) return FR_OK;
+    if (g_scratch == nullptr) FR_REFUSE("token_input: no scratch for the gated table rows");
     const size_t smem = (size_t)(dim + width) * sizeof(float);
     if (smem > 200 * 1024) FR_REFUSE("token_input: width %d and dim %d need more shared memory than an SM has", width, dim);
     FrVec nv{norm, norm_dtype};
+    const int gate_blocks = (int)(((long long)n_rows * dim + 3) / 4);
+    const int threads = n_rows < 128 ? 1024 : 256;            // few rows: more threads each, to keep loads in flight
     if (w_dtype == FR_F32) {
-        if (smem > 48 * 1024) FR_CUDA(cudaFuncSetAttribute(token_input_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-        FR_CUDA(fr_launch(token_input_kernel<float>, dim3(n_rows), dim3(256), smem, stream, x, tokens, row_seq, (const float*)table,
-                          table_ld, col0, vocab, (const float*)gate, (const float*)proj, nv, width, dim, eps));
+        FR_CUDA(fr_launch(token_gate_kernel<float>, dim3(gate_blocks), dim3(128), 0, stream, (const float*)x, tokens, row_seq,
+                          (const float*)table, table_ld, col0, vocab, (const float*)gate, g_scratch, n_rows, width, dim));
+        if (smem > 48 * 1024) FR_CUDA(cudaFuncSetAttribute(token_proj_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+        FR_CUDA(fr_launch(token_proj_kernel<float>, dim3(n_rows), dim3(threads), smem, stream, x, tokens, row_seq, vocab,
+                          (const float*)g_scratch, (const float*)proj, nv, width, dim, eps));
     } else if (w_dtype == FR_BF16) {
-        if (smem > 48 * 1024) FR_CUDA(cudaFuncSetAttribute(token_input_kernel<bf16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-        FR_CUDA(fr_launch(token_input_kernel<bf16>, dim3(n_rows), dim3(256), smem, stream, x, tokens, row_seq, (const bf16*)table,
-                          table_ld, col0, vocab, (const bf16*)gate, (const bf16*)proj, nv, width, dim, eps));
+        FR_CUDA(fr_launch(token_gate_kernel<bf16>, dim3(gate_blocks), dim3(128), 0, stream, (const float*)x, tokens, row_seq,
+                          (const bf16*)table, table_ld, col0, vocab, (const bf16*)gate, g_scratch, n_rows, width, dim));
+        if (smem > 48 * 1024) FR_CUDA(cudaFuncSetAttribute(token_proj_kernel<bf16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+        FR_CUDA(fr_launch(token_proj_kernel<bf16>, dim3(n_rows), dim3(threads), smem, stream, x, tokens, row_seq, vocab,
+                          (const float*)g_scratch, (const bf16*)proj, nv, width, dim, eps));
     } else {
         FR_REFUSE("token_input: unknown dtype %d", w_dtype);
     }
     FR_CHECK_LAUNCH("token_input");
+    return FR_OK;
+}
+
+FR_EXPORT int residual_gelu_table(const float* z, const int* tokens, const void* table, int table_ld, int col0, int vocab, void* g,
+                                  int rows, int dim, int w_dtype, cudaStream_t stream) {
+    if (rows <= 0 || dim <= 0) return FR_OK;
+    const int blocks = blocks_for((long long)rows * dim);
+    if (w_dtype == FR_F32) FR_CUDA(fr_launch(gelu_table_kernel<float>, dim3(blocks), dim3(256), 0, stream, z, tokens, (const float*)table, table_ld, col0, vocab, (float*)g, rows, dim));
+    else if (w_dtype == FR_BF16) FR_CUDA(fr_launch(gelu_table_kernel<bf16>, dim3(blocks), dim3(256), 0, stream, z, tokens, (const bf16*)table, table_ld, col0, vocab, (bf16*)g, rows, dim));
+    else FR_REFUSE("gelu_table: unknown dtype %d", w_dtype);
+    FR_CHECK_LAUNCH("gelu_table");
+    return FR_OK;
+}
+
+FR_EXPORT int residual_rms_add(float* x, const float* y, const void* norm, int norm_dtype, int rows, int width, float eps, cudaStream_t stream) {
+    if (rows <= 0) return FR_OK;
+    FR_CUDA(fr_launch(rms_add_kernel, dim3(rows), dim3(256), 0, stream, x, y, FrVec{norm, norm_dtype}, width, eps));
+    FR_CHECK_LAUNCH("rms_add");
     return FR_OK;
 }

@@ -95,16 +95,37 @@ route_kernel(const float* __restrict__ logits, int ld, int rows, int experts, in
     }
 }
 
+// one row per blockIdx.y; eight consecutive channels per thread where rows allow 16-byte pieces
 template <typename T>
-__global__ void scale_by_route_kernel(T* __restrict__ act, const float* __restrict__ dense, int experts, int inner, long long n) {
+__global__ void scale_by_route_kernel(T* __restrict__ act, const float* __restrict__ dense, int rows, int experts, int inner, int by_eight) {
     fr_pdl_wait();
     fr_pdl_launch();
-    const long long per_row = (long long)experts * inner;
-    for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (long long)gridDim.x * blockDim.x) {
-        const long long row = i / per_row;
-        const int e = (int)((i - row * per_row) / inner);
-        fr_store(act + i, fr_load(act + i) * dense[row * experts + e]);
+    const int per_row = experts * inner;
+  for (int row = blockIdx.y; row < rows; row += gridDim.y) {
+    T* a = act + (size_t)row * per_row;
+    const float* d = dense + (size_t)row * experts;
+    if (by_eight) {
+        if constexpr (sizeof(T) == 2) {
+            for (int c = (blockIdx.x * blockDim.x + threadIdx.x) * 8; c < per_row; c += gridDim.x * blockDim.x * 8) {
+                const float w = d[c / inner];
+                uint4 v = *(const uint4*)(a + c);
+                if (w == 0.f) v = make_uint4(0, 0, 0, 0);
+                else {
+                    __nv_bfloat162* h = (__nv_bfloat162*)&v;
+#pragma unroll
+                    for (int i = 0; i < 4; ++i) {
+                        const float2 f = __bfloat1622float2(h[i]);
+                        h[i] = __floats2bfloat162_rn(f.x * w, f.y * w);
+                    }
+                }
+                *(uint4*)(a + c) = v;
+            }
+            continue;
+        }
     }
+    for (int c = blockIdx.x * blockDim.x + threadIdx.x; c < per_row; c += gridDim.x * blockDim.x)
+        fr_store(a + c, fr_load(a + c) * d[c / inner]);
+  }
 }
 
 // block: one (row, choice) and a tile of `inner`; a warp per inner channel, lanes over the width
@@ -138,6 +159,181 @@ gate_up_kernel(const T* __restrict__ h, const int* __restrict__ ids, const T* __
     }
 }
 
+// Few rows: a block owns one expert and a tile of `inner`; it gathers the rows that chose the expert (at most MAX_SHARE,
+// staged in shared memory in their own dtype) and reads every weight row once for all of them, 16 bytes per lane.
+constexpr int MAX_SHARE = 16;
+
+template <typename T>
+__global__ void __launch_bounds__(256)
+gate_up_by_expert_kernel(const T* __restrict__ h, const int* __restrict__ ids, const T* __restrict__ w_gate_up, T* __restrict__ act,
+                         int rows, int top, int width, int inner, int per_block) {
+    extern __shared__ __align__(16) unsigned char raw[];
+    T* hs = (T*)raw;                           // [MAX_SHARE][width]
+    __shared__ int pairs[MAX_SHARE];
+    __shared__ int n_pairs;
+    constexpr int PER = 16 / sizeof(T);
+    fr_pdl_wait();
+    fr_pdl_launch();
+    const int e = blockIdx.x;
+    // the pairs that chose this expert, in order: the ids are read side by side, then one thread lists the matches
+    __shared__ int chosen[MAX_SHARE * 32];
+    for (int pr = threadIdx.x; pr < rows * top; pr += blockDim.x) chosen[pr] = ids[pr];
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        int n = 0;
+        for (int pr = 0; pr < rows * top && n < MAX_SHARE; ++pr)
+            if (chosen[pr] == e) pairs[n++] = pr;
+        n_pairs = n;
+    }
+    __syncthreads();
+    const int n = n_pairs;
+    if (n == 0) return;
+    for (int idx = threadIdx.x; idx < n * (width / PER); idx += blockDim.x) {
+        const int r = idx / (width / PER), c = idx % (width / PER);
+        ((uint4*)(hs + (size_t)r * width))[c] = ((const uint4*)(h + (size_t)(pairs[r] / top) * width))[c];
+    }
+    __syncthreads();
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int f0 = blockIdx.y * per_block;
+    const T* w = w_gate_up + (size_t)e * 2 * inner * width;
+    for (int f = f0 + warp; f < min(f0 + per_block, inner); f += 8) {
+        const uint4* g4 = (const uint4*)(w + (size_t)(2 * f) * width);
+        const uint4* u4 = (const uint4*)(w + (size_t)(2 * f + 1) * width);
+        float sg[MAX_SHARE], su[MAX_SHARE];
+#pragma unroll
+        for (int r = 0; r < MAX_SHARE; ++r) sg[r] = su[r] = 0.f;
+        for (int c0 = lane; c0 < width / PER; c0 += 32 * 4) {
+            uint4 gv[4], uv[4];                   // four pieces of each row in flight
+#pragma unroll
+            for (int k = 0; k < 4; ++k) {
+                const int c = c0 + 32 * k;
+                if (c < width / PER) {
+                    gv[k] = __ldg(g4 + c);
+                    uv[k] = __ldg(u4 + c);
+                }
+            }
+#pragma unroll
+            for (int k = 0; k < 4; ++k) {
+                const int c = c0 + 32 * k;
+                if (c >= width / PER) break;
+                float gf[PER], uf[PER];
+#pragma unroll
+                for (int i = 0; i < PER; ++i) {
+                    gf[i] = fr_load((const T*)&gv[k] + i);
+                    uf[i] = fr_load((const T*)&uv[k] + i);
+                }
+#pragma unroll
+                for (int r = 0; r < MAX_SHARE; ++r) {
+                    if (r < n) {
+                        const uint4 hv = ((const uint4*)(hs + (size_t)r * width))[c];
+#pragma unroll
+                        for (int i = 0; i < PER; ++i) {
+                            const float x = fr_load((const T*)&hv + i);
+                            sg[r] = fmaf(x, gf[i], sg[r]);
+                            su[r] = fmaf(x, uf[i], su[r]);
+                        }
+                    }
+                }
+            }
+        }
+#pragma unroll
+        for (int r = 0; r < MAX_SHARE; ++r) {
+            if (r < n) {
+                const float a = fr_warp_sum(sg[r]), b = fr_warp_sum(su[r]);
+                if (lane == 0) fr_store(act + (size_t)pairs[r] * inner + f, a / (1.0f + expf(-a)) * b);
+            }
+        }
+    }
+}
+
+// The same for the down product: a block owns one expert and a tile of output columns, stages the activations of the
+// (row, choice) pairs that chose the expert, reads every weight row once for all of them and leaves each pair's part
+// [pairs][width] in fp32; combine_kernel then adds the parts to the residual in the order of the choices, so the sum
+// does not depend on which block finished first.
+template <typename T>
+__global__ void __launch_bounds__(256)
+down_by_expert_kernel(const T* __restrict__ act, const int* __restrict__ ids, const T* __restrict__ w_down, int ld_down,
+                      float* __restrict__ part, int rows, int top, int width, int inner, int per_block) {
+    extern __shared__ __align__(16) unsigned char raw[];
+    T* as = (T*)raw;                           // [MAX_SHARE][inner]
+    __shared__ int pairs[MAX_SHARE];
+    __shared__ int n_pairs;
+    constexpr int PER = 16 / sizeof(T);
+    fr_pdl_wait();
+    fr_pdl_launch();
+    const int e = blockIdx.x;
+    // the pairs that chose this expert, in order: the ids are read side by side, then one thread lists the matches
+    __shared__ int chosen[MAX_SHARE * 32];
+    for (int pr = threadIdx.x; pr < rows * top; pr += blockDim.x) chosen[pr] = ids[pr];
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        int n = 0;
+        for (int pr = 0; pr < rows * top && n < MAX_SHARE; ++pr)
+            if (chosen[pr] == e) pairs[n++] = pr;
+        n_pairs = n;
+    }
+    __syncthreads();
+    const int n = n_pairs;
+    if (n == 0) return;
+    for (int idx = threadIdx.x; idx < n * (inner / PER); idx += blockDim.x) {
+        const int r = idx / (inner / PER), c = idx % (inner / PER);
+        ((uint4*)(as + (size_t)r * inner))[c] = ((const uint4*)(act + (size_t)pairs[r] * inner))[c];
+    }
+    __syncthreads();
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int c0 = blockIdx.y * per_block;
+    for (int col = c0 + warp; col < min(c0 + per_block, width); col += 8) {
+        const uint4* w4 = (const uint4*)(w_down + (size_t)col * ld_down + (size_t)e * inner);
+        float acc[MAX_SHARE];
+#pragma unroll
+        for (int r = 0; r < MAX_SHARE; ++r) acc[r] = 0.f;
+        for (int f0 = lane; f0 < inner / PER; f0 += 32 * 4) {
+            uint4 wv[4];
+#pragma unroll
+            for (int k = 0; k < 4; ++k)
+                if (f0 + 32 * k < inner / PER) wv[k] = __ldg(w4 + f0 + 32 * k);
+#pragma unroll
+            for (int k = 0; k < 4; ++k) {
+                const int f = f0 + 32 * k;
+                if (f >= inner / PER) break;
+                float wf[PER];
+#pragma unroll
+                for (int i = 0; i < PER; ++i) wf[i] = fr_load((const T*)&wv[k] + i);
+#pragma unroll
+                for (int r = 0; r < MAX_SHARE; ++r) {
+                    if (r < n) {
+                        const uint4 av = ((const uint4*)(as + (size_t)r * inner))[f];
+#pragma unroll
+                        for (int i = 0; i < PER; ++i) acc[r] = fmaf(fr_load((const T*)&av + i), wf[i], acc[r]);
+                    }
+                }
+            }
+        }
+#pragma unroll
+        for (int r = 0; r < MAX_SHARE; ++r) {
+            if (r < n) {
+                const float v = fr_warp_sum(acc[r]);
+                if (lane == 0) part[(size_t)pairs[r] * width + col] = v;
+            }
+        }
+    }
+}
+
+template <typename TR>
+__global__ void combine_kernel(const float* __restrict__ part, const int* __restrict__ ids, const float* __restrict__ weights,
+                               const TR* __restrict__ residual, TR* __restrict__ out, int top, int width) {
+    fr_pdl_wait();
+    fr_pdl_launch();
+    const int row = blockIdx.y;
+    for (int c = blockIdx.x * blockDim.x + threadIdx.x; c < width; c += gridDim.x * blockDim.x) {
+        float total = 0.f;
+        for (int j = 0; j < top; ++j)
+            if (ids[(size_t)row * top + j] >= 0) total = fmaf(weights[(size_t)row * top + j], part[((size_t)row * top + j) * width + c], total);
+        const float r = residual != nullptr ? fr_load(residual + (size_t)row * width + c) : 0.f;
+        fr_store(out + (size_t)row * width + c, r + total);
+    }
+}
+
 // block: one row and a tile of the width; a warp per output column, lanes over inner
 template <typename T, typename TR>
 __global__ void __launch_bounds__(256)
@@ -159,7 +355,16 @@ down_combine_kernel(const T* __restrict__ act, const int* __restrict__ ids, cons
             if (e < 0) continue;
             const T* w = w_down + (size_t)c * ld_down + (size_t)e * inner;
             float s = 0.f;
-            for (int f = lane; f < inner; f += 32) s = fmaf(as[j * inner + f], fr_load(w + f), s);
+            constexpr int PER = 16 / sizeof(T);
+            if (inner % PER == 0 && (((uintptr_t)w) & 15) == 0) {
+                for (int f = lane * PER; f < inner; f += 32 * PER) {
+                    const uint4 wv = *(const uint4*)(w + f);
+#pragma unroll
+                    for (int i = 0; i < PER; ++i) s = fmaf(as[j * inner + f + i], fr_load((const T*)&wv + i), s);
+                }
+            } else {
+                for (int f = lane; f < inner; f += 32) s = fmaf(as[j * inner + f], fr_load(w + f), s);
+            }
             total = fmaf(weights[(size_t)row * top + j], fr_warp_sum(s), total);
         }
         if (lane == 0) {
@@ -183,25 +388,48 @@ FR_EXPORT int routed_route(const float* logits, int ld, int rows, int experts, i
 }
 
 FR_EXPORT int routed_scale_by_route(void* act, const float* dense, int rows, int experts, int inner, int dtype, cudaStream_t stream) {
-    const long long n = (long long)rows * experts * inner;
-    if (n <= 0) return FR_OK;
-    const long long cap = (long long)(fr_sm_count() > 0 ? fr_sm_count() : 128) * 16;
-    const int blocks = (int)((n + 255) / 256 < cap ? (n + 255) / 256 : cap);
-    if (dtype == FR_F32) FR_CUDA(fr_launch(scale_by_route_kernel<float>, dim3(blocks), dim3(256), 0, stream, (float*)act, dense, experts, inner, n));
-    else if (dtype == FR_BF16) FR_CUDA(fr_launch(scale_by_route_kernel<bf16>, dim3(blocks), dim3(256), 0, stream, (bf16*)act, dense, experts, inner, n));
+    if (rows <= 0 || experts <= 0 || inner <= 0) return FR_OK;
+    const long long per_row = (long long)experts * inner;
+    if (per_row > 0x7fffffffLL) FR_REFUSE("scale_by_route: %lld channels per row", per_row);
+    const int by_eight = dtype == FR_BF16 && inner % 8 == 0 && (((uintptr_t)act) & 15) == 0;
+    const long long items = by_eight ? per_row / 8 : per_row;
+    const int bx = (int)((items + 255) / 256 < 64 ? (items + 255) / 256 : 64);
+    if (dtype == FR_F32) FR_CUDA(fr_launch(scale_by_route_kernel<float>, dim3(bx, rows < 65535 ? rows : 65535), dim3(256), 0, stream, (float*)act, dense, rows, experts, inner, 0));
+    else if (dtype == FR_BF16) FR_CUDA(fr_launch(scale_by_route_kernel<bf16>, dim3(bx, rows < 65535 ? rows : 65535), dim3(256), 0, stream, (bf16*)act, dense, rows, experts, inner, by_eight));
     else FR_REFUSE("scale_by_route: unknown dtype %d", dtype);
     FR_CHECK_LAUNCH("scale_by_route");
     return FR_OK;
 }
 
-FR_EXPORT int routed_gate_up(const void* h, const int* ids, const void* w_gate_up, void* act, int rows, int top, int width, int inner,
-                             int dtype, cudaStream_t stream) {
+FR_EXPORT int routed_gate_up(const void* h, const int* ids, const void* w_gate_up, void* act, int rows, int top, int experts, int width,
+                             int inner, int dtype, cudaStream_t stream) {
     if (rows <= 0) return FR_OK;
     const size_t smem = (size_t)width * sizeof(float);
     if (smem > 200 * 1024) FR_REFUSE("gate_up: width %d does not fit an SM's shared memory", width);
     const int per_block = inner < 64 ? inner : 64;
     const dim3 grid(rows * top, (inner + per_block - 1) / per_block);
     if (grid.y > 65535) FR_REFUSE("gate_up: inner size %d", inner);
+    // few rows: one block per (expert, tile) reads the weights once for all rows that chose the expert
+    const size_t esize = dtype == FR_F32 ? 4 : 2;
+    const size_t share = (size_t)(rows < MAX_SHARE ? rows : MAX_SHARE) * width * esize;     // rows that can choose one expert
+    if (dtype == FR_BF16 && rows <= MAX_SHARE && experts > 0 && width % (16 / esize) == 0 && share <= 160 * 1024 &&
+        ((((uintptr_t)h) | ((uintptr_t)w_gate_up)) & 15) == 0) {
+        const int eper = 16;                     // 16 inner channels per block: enough blocks to fill the device
+        const dim3 eg(experts, (inner + eper - 1) / eper);
+        if (dtype == FR_F32) {
+            if (share > 48 * 1024) FR_CUDA(cudaFuncSetAttribute(gate_up_by_expert_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)share));
+            FR_CUDA(fr_launch(gate_up_by_expert_kernel<float>, eg, dim3(256), share, stream, (const float*)h, ids, (const float*)w_gate_up,
+                              (float*)act, rows, top, width, inner, eper));
+        } else if (dtype == FR_BF16) {
+            if (share > 48 * 1024) FR_CUDA(cudaFuncSetAttribute(gate_up_by_expert_kernel<bf16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)share));
+            FR_CUDA(fr_launch(gate_up_by_expert_kernel<bf16>, eg, dim3(256), share, stream, (const bf16*)h, ids, (const bf16*)w_gate_up,
+                              (bf16*)act, rows, top, width, inner, eper));
+        } else {
+            FR_REFUSE("gate_up: unknown dtype %d", dtype);
+        }
+        FR_CHECK_LAUNCH("gate_up (by expert)");
+        return FR_OK;
+    }
     if (dtype == FR_F32) {
         if (smem > 48 * 1024) FR_CUDA(cudaFuncSetAttribute(gate_up_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
         FR_CUDA(fr_launch(gate_up_kernel<float>, grid, dim3(256), smem, stream, (const float*)h, ids, (const float*)w_gate_up,
@@ -217,11 +445,35 @@ FR_EXPORT int routed_gate_up(const void* h, const int* ids, const void* w_gate_u
     return FR_OK;
 }
 
+// Floats of scratch that routed_down_combine wants for these sizes (0: none).
+FR_EXPORT long long routed_down_scratch_floats(int rows, int top, int width, int inner, int dtype) {
+    const size_t share = (size_t)(rows < MAX_SHARE ? rows : MAX_SHARE) * inner * 2;
+    if (dtype == FR_BF16 && rows <= MAX_SHARE && inner % 8 == 0 && share <= 160 * 1024) return (long long)rows * top * width;
+    return 0;
+}
+
 // residual and out [rows][width] in res_dtype (fp32 for a 32-bit residual stream); residual may be null.
 FR_EXPORT int routed_down_combine(const void* act, const int* ids, const float* weights, const void* w_down, int ld_down,
-                                  const void* residual, void* out, int res_dtype, int rows, int top, int width, int inner, int dtype,
-                                  cudaStream_t stream) {
+                                  const void* residual, void* out, int res_dtype, int rows, int top, int experts, int width, int inner,
+                                  float* scratch, int dtype, cudaStream_t stream) {
     if (rows <= 0) return FR_OK;
+    if (scratch != nullptr && routed_down_scratch_floats(rows, top, width, inner, dtype) > 0 && experts > 0 && ld_down % 8 == 0 &&
+        ((((uintptr_t)act) | ((uintptr_t)w_down)) & 15) == 0 && rows <= 65535) {
+        const size_t share = (size_t)(rows < MAX_SHARE ? rows : MAX_SHARE) * inner * 2;
+        const int per = 16;
+        if (share > 48 * 1024) FR_CUDA(cudaFuncSetAttribute(down_by_expert_kernel<bf16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)share));
+        FR_CUDA(fr_launch(down_by_expert_kernel<bf16>, dim3(experts, (width + per - 1) / per), dim3(256), share, stream, (const bf16*)act, ids,
+                          (const bf16*)w_down, ld_down, scratch, rows, top, width, inner, per));
+        FR_CHECK_LAUNCH("down (by expert)");
+        const dim3 cg((width + 255) / 256, rows);
+        if (res_dtype == FR_F32) FR_CUDA(fr_launch(combine_kernel<float>, cg, dim3(256), 0, stream, (const float*)scratch, ids, weights,
+                                                   (const float*)residual, (float*)out, top, width));
+        else if (res_dtype == FR_BF16) FR_CUDA(fr_launch(combine_kernel<bf16>, cg, dim3(256), 0, stream, (const float*)scratch, ids, weights,
+                                                         (const bf16*)residual, (bf16*)out, top, width));
+        else FR_REFUSE("down_combine: unknown residual dtype %d", res_dtype);
+        FR_CHECK_LAUNCH("combine");
+        return FR_OK;
+    }
     const size_t smem = (size_t)top * inner * sizeof(float);
     if (smem > 200 * 1024) FR_REFUSE("down_combine: top %d x inner %d does not fit an SM's shared memory", top, inner);
     const int per_block = width < 64 ? width : 64;

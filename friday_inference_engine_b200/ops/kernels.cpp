@@ -102,13 +102,16 @@ FAMILY(AttentionWindow, attention_window, "attention_window", resolve(h, fam, "a
        resolve(h, fam, "attention_window", t.run);)
 FAMILY(Residual, residual, "residual", resolve(h, fam, "residual_norm_cast", t.norm_cast);
        resolve(h, fam, "residual_concat_cast", t.concat_cast); resolve(h, fam, "residual_add_scaled", t.add_scaled);
-       resolve(h, fam, "residual_kv_store", t.kv_store); resolve(h, fam, "residual_token_input", t.token_input);)
+       resolve(h, fam, "residual_kv_store", t.kv_store); resolve(h, fam, "residual_token_input", t.token_input);
+       resolve(h, fam, "residual_gelu_table", t.gelu_table); resolve(h, fam, "residual_rms_add", t.rms_add);)
 FAMILY(Recurrence, recurrence, "recurrence", resolve(h, fam, "recurrence_shift_mix", t.shift_mix);
        resolve(h, fam, "recurrence_tanh_rows", t.tanh_rows); resolve(h, fam, "recurrence_scan", t.scan);
+       resolve(h, fam, "recurrence_scan_plan", t.scan_plan);
        resolve(h, fam, "recurrence_head_norm_gate", t.head_norm_gate);)
 FAMILY(Routed, routed, "routed", resolve(h, fam, "routed_route", t.route);
        resolve(h, fam, "routed_scale_by_route", t.scale_by_route); resolve(h, fam, "routed_gate_up", t.gate_up);
-       resolve(h, fam, "routed_down_combine", t.down_combine);)
+       resolve(h, fam, "routed_down_combine", t.down_combine);
+       resolve(h, fam, "routed_down_scratch_floats", t.down_scratch_floats);)
 FAMILY(AttentionMma, attention_mma, "attention_mma", resolve(h, fam, "attention_mma", t.run);
        resolve(h, fam, "attention_mma_clusters_at_once", t.clusters_at_once);)
 FAMILY(AttentionTc, attention_tc, "attention_tc", resolve(h, fam, "attention_tc", t.run);)

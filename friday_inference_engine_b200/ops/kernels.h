@@ -62,7 +62,9 @@ struct Residual {
     int (*kv_store)(const void*, int, int, int, int, int, int, const int*, const int*, void*, void*, const int*, int, int, int, int,
                     cudaStream_t);
     int (*token_input)(float*, const int*, const int*, const void*, int, int, int, const void*, const void*, const void*, int, int,
-                       int, int, float, int, cudaStream_t);
+                       int, int, float, float*, int, cudaStream_t);
+    int (*gelu_table)(const float*, const int*, const void*, int, int, int, void*, int, int, int, cudaStream_t);
+    int (*rms_add)(float*, const float*, const void*, int, int, int, float, cudaStream_t);
 };
 struct Recurrence {
     last_error_fn last_error;
@@ -71,7 +73,8 @@ struct Recurrence {
     int (*tanh_rows)(void*, long long, int, cudaStream_t);
     int (*scan)(const void*, int, const void*, int, const void*, int, const float*, const void*, int, const void*, int, float*,
                 float*, long long, long long, const void*, int, const int*, const int*, const int*, const int*, int, int, int, int,
-                int, int, float, float, int, cudaStream_t);
+                int, int, float, float, int, float*, int, cudaStream_t);
+    int (*scan_plan)(int, int, int, int, int, long long*);
     int (*head_norm_gate)(const float*, const void*, int, void*, const void*, int, int, const int*, int, int, int, float, float, int,
                           cudaStream_t);
 };
@@ -79,9 +82,10 @@ struct Routed {
     last_error_fn last_error;
     int (*route)(const float*, int, int, int, int, int, int*, float*, float*, cudaStream_t);
     int (*scale_by_route)(void*, const float*, int, int, int, int, cudaStream_t);
-    int (*gate_up)(const void*, const int*, const void*, void*, int, int, int, int, int, cudaStream_t);
+    int (*gate_up)(const void*, const int*, const void*, void*, int, int, int, int, int, int, cudaStream_t);
     int (*down_combine)(const void*, const int*, const float*, const void*, int, const void*, void*, int, int, int, int, int, int,
-                        cudaStream_t);
+                        float*, int, cudaStream_t);
+    long long (*down_scratch_floats)(int, int, int, int, int);
 };
 struct AttentionMma {
     last_error_fn last_error;

@@ -252,10 +252,34 @@ void Ops::token_input(Tensor& x, const StepContext& ctx, const Tensor& table, in
         col0 < 0 || col0 + dim > table.cols() || gate.dtype != table.dtype || proj.dtype != table.dtype)
         throw KernelError("token_input: gate [dim, width], proj [width, dim], norm [width] and a table slice of dim columns, one dtype");
     const auto& k = kernels::residual();
+    if (x.rows() > 64 && table.dtype == DType::BF16 && dim % 8 == 0 && x.cols() % 8 == 0) {
+        // many rows: both projections as products on the tensor cores (the stream rounded to bf16 for the first, as
+        // for every other product), the steps between them row-wise
+        Tensor xb = alloc(DType::BF16, x.rows(), x.cols());
+        {
+            Timed t(*this, Other);
+            call(launches_, k, k.concat_cast(x.data, x.data, code(x.dtype), xb.data, code(DType::BF16), (int)x.rows(), (int)x.cols(), 0, stream_),
+                 "concat_cast");
+        }
+        Tensor z = linear(Rows(xb), gate, nullptr, nullptr, (int)DType::F32);
+        Tensor g = alloc(DType::BF16, x.rows(), dim);
+        {
+            Timed t(*this, Other);
+            call(launches_, k, k.gelu_table((const float*)z.data, ctx.tokens, table.data, (int)table.ld, (int)col0, (int)table.rows(), g.data,
+                                            (int)x.rows(), (int)dim, code(table.dtype), stream_), "gelu_table");
+        }
+        Tensor y = linear(Rows(g), proj, nullptr, nullptr, (int)DType::F32);
+        Timed t(*this, Other);
+        call(launches_, k, k.rms_add((float*)x.data, (const float*)y.data, norm.data, code(norm.dtype), (int)x.rows(), (int)x.cols(), eps, stream_),
+             "rms_add");
+        return;
+    }
+    float* g = scratch_floats(x.rows() * dim);
     Timed t(*this, Other);
     call(launches_, k, k.token_input((float*)x.data, ctx.tokens, ctx.row_seq, table.data, (int)table.ld, (int)col0, (int)table.rows(),
-                                     gate.data, proj.data, norm.data, code(norm.dtype), (int)x.rows(), (int)x.cols(), (int)dim, eps,
+                                     gate.data, proj.data, norm.data, code(norm.dtype), (int)x.rows(), (int)x.cols(), (int)dim, eps, g,
                                      code(table.dtype), stream_), "token_input");
+    ++launches_;
 }
 
 // ------------------------------------------------------------------ mixers with a matrix state
@@ -294,13 +318,16 @@ Tensor Ops::state_scan(const Tensor& q, const Tensor& kk, const Tensor& v, const
     if (s.state_offset + (long long)s.heads * s.dk * s.dv > stride) throw KernelError("state_scan: the state is smaller than the heads' matrices");
     Tensor out = alloc(DType::F32, q.rows(), (int64_t)s.heads * s.dv);
     const auto& k = kernels::recurrence();
+    long long seg_floats = 0;
+    const int seg_len = k.scan_plan(ctx.n_seqs, ctx.max_q_len, s.heads, s.dk, s.dv, &seg_floats);
+    float* seg_scratch = seg_len > 0 ? scratch_floats(seg_floats) : nullptr;
     Timed t(*this, Attention);
     call(launches_, k,
          k.scan(q.data, (int)q.ld, kk.data, (int)kk.ld, v.data, (int)v.ld, (const float*)z.data, s.z_bias ? s.z_bias->data : nullptr,
                 s.z_bias ? code(s.z_bias->dtype) : 0, s.bonus ? s.bonus->data : nullptr, s.bonus ? code(s.bonus->dtype) : 0,
                 (float*)out.data, (float*)view.state.data, stride, (long long)s.state_offset, s.carry ? s.carry->data : nullptr,
                 s.carry ? (int)s.carry->cols() : 0, ctx.row_seq, ctx.seq_start, ctx.seq_qlen, view.seq_slots, ctx.n_seqs,
-                ctx.max_q_len, s.heads, s.dk, s.dv, s.mode, s.q_scale, s.tau, code(q.dtype), stream_),
+                ctx.max_q_len, s.heads, s.dk, s.dv, s.mode, s.q_scale, s.tau, seg_len, seg_scratch, code(q.dtype), stream_),
          "scan");
     return out;
 }
@@ -348,8 +375,8 @@ Tensor Ops::expert_gate_up(const Tensor& h, const Routing& r, const Tensor& w_ga
     Tensor act = alloc(h.dtype, h.rows() * top, inner);
     const auto& k = kernels::routed();
     Timed t(*this, Product);
-    call(launches_, k, k.gate_up(h.data, (const int*)r.ids.data, w_gate_up.data, act.data, (int)h.rows(), top, (int)h.cols(), inner,
-                                 code(h.dtype), stream_), "gate_up");
+    call(launches_, k, k.gate_up(h.data, (const int*)r.ids.data, w_gate_up.data, act.data, (int)h.rows(), top,
+                                 (int)(w_gate_up.rows() / (2 * (int64_t)inner)), (int)h.cols(), inner, code(h.dtype), stream_), "gate_up");
     return act;
 }
 
@@ -357,10 +384,14 @@ Tensor Ops::expert_down_combine(const Tensor& act, const Routing& r, const Tenso
     if (act.dtype != w_down.dtype) throw KernelError("expert_down_combine: activations and weights of one dtype");
     Tensor out = alloc(residual.dtype, residual.rows(), residual.cols());
     const auto& k = kernels::routed();
+    const long long need = k.down_scratch_floats((int)residual.rows(), top, (int)residual.cols(), inner, code(act.dtype));
+    float* scratch = need > 0 ? scratch_floats(need) : nullptr;
     Timed t(*this, Product);
     call(launches_, k, k.down_combine(act.data, (const int*)r.ids.data, (const float*)r.weights.data, w_down.data, (int)w_down.ld,
-                                      residual.data, out.data, code(residual.dtype), (int)residual.rows(), top, (int)residual.cols(),
-                                      inner, code(act.dtype), stream_), "down_combine");
+                                      residual.data, out.data, code(residual.dtype), (int)residual.rows(), top,
+                                      (int)(w_down.cols() / inner), (int)residual.cols(), inner, scratch, code(act.dtype), stream_),
+         "down_combine");
+    if (need > 0) ++launches_;
     return out;
 }
 

@@ -319,18 +319,60 @@ down_by_expert_kernel(const T* __restrict__ act, const int* __restrict__ ids, co
     }
 }
 
+// part: one row per (row, choice) pair, at the pair's own index or, with `pos`, at pos[pair] (pairs sorted by expert)
 template <typename TR>
 __global__ void combine_kernel(const float* __restrict__ part, const int* __restrict__ ids, const float* __restrict__ weights,
-                               const TR* __restrict__ residual, TR* __restrict__ out, int top, int width) {
+                               const int* __restrict__ pos, const TR* __restrict__ residual, TR* __restrict__ out, int rows, int top,
+                               int width) {
     fr_pdl_wait();
     fr_pdl_launch();
-    const int row = blockIdx.y;
+  for (int row = blockIdx.y; row < rows; row += gridDim.y) {
     for (int c = blockIdx.x * blockDim.x + threadIdx.x; c < width; c += gridDim.x * blockDim.x) {
         float total = 0.f;
-        for (int j = 0; j < top; ++j)
-            if (ids[(size_t)row * top + j] >= 0) total = fmaf(weights[(size_t)row * top + j], part[((size_t)row * top + j) * width + c], total);
+        for (int j = 0; j < top; ++j) {
+            const size_t pair = (size_t)row * top + j;
+            if (ids[pair] >= 0) total = fmaf(weights[pair], part[(size_t)(pos != nullptr ? pos[pair] : (int)pair) * width + c], total);
+        }
         const float r = residual != nullptr ? fr_load(residual + (size_t)row * width + c) : 0.f;
         fr_store(out + (size_t)row * width + c, r + total);
+    }
+  }
+}
+
+// The (row, choice) pairs in the order of their experts: offsets[e] .. offsets[e + 1] are expert e's places, pos[pair] the
+// pair's place, row_at[place] the row whose activations belong there.  Which of an expert's places a pair gets depends on
+// scheduling; no result depends on it, since every place is computed from its own row alone.  One block.
+__global__ void __launch_bounds__(1024) sort_pairs_kernel(const int* __restrict__ ids, int n_pairs, int top, int experts,
+                                                          int* __restrict__ offsets, int* __restrict__ pos, int* __restrict__ row_at) {
+    __shared__ int cnt[256], off[257], cur[256];
+    fr_pdl_wait();
+    fr_pdl_launch();
+    for (int e = threadIdx.x; e < experts; e += blockDim.x) cnt[e] = cur[e] = 0;
+    __syncthreads();
+    for (int p = threadIdx.x; p < n_pairs; p += blockDim.x) {
+        const int e = ids[p];
+        if (e >= 0 && e < experts) atomicAdd(&cnt[e], 1);
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        int at = 0;
+        for (int e = 0; e < experts; ++e) {
+            off[e] = at;
+            at += cnt[e];
+        }
+        off[experts] = at;
+    }
+    __syncthreads();
+    for (int e = threadIdx.x; e <= experts; e += blockDim.x) offsets[e] = off[e];
+    for (int p = threadIdx.x; p < n_pairs; p += blockDim.x) {
+        const int e = ids[p];
+        if (e >= 0 && e < experts) {
+            const int place = off[e] + atomicAdd(&cur[e], 1);
+            pos[p] = place;
+            row_at[place] = p / top;
+        } else {
+            pos[p] = 0;
+        }
     }
 }
 
@@ -467,9 +509,9 @@ FR_EXPORT int routed_down_combine(const void* act, const int* ids, const float* 
         FR_CHECK_LAUNCH("down (by expert)");
         const dim3 cg((width + 255) / 256, rows);
         if (res_dtype == FR_F32) FR_CUDA(fr_launch(combine_kernel<float>, cg, dim3(256), 0, stream, (const float*)scratch, ids, weights,
-                                                   (const float*)residual, (float*)out, top, width));
+                                                   (const int*)nullptr, (const float*)residual, (float*)out, rows, top, width));
         else if (res_dtype == FR_BF16) FR_CUDA(fr_launch(combine_kernel<bf16>, cg, dim3(256), 0, stream, (const float*)scratch, ids, weights,
-                                                         (const bf16*)residual, (bf16*)out, top, width));
+                                                         (const int*)nullptr, (const bf16*)residual, (bf16*)out, rows, top, width));
         else FR_REFUSE("down_combine: unknown residual dtype %d", res_dtype);
         FR_CHECK_LAUNCH("combine");
         return FR_OK;
@@ -492,5 +534,28 @@ FR_EXPORT int routed_down_combine(const void* act, const int* ids, const float* 
     else FR_REFUSE("down_combine: no kernel for dtypes %d and %d", dtype, res_dtype);
 #undef DOWN
     FR_CHECK_LAUNCH("down_combine");
+    return FR_OK;
+}
+
+// offsets [experts + 1], pos [rows * top], row_at [rows * top]: see sort_pairs_kernel.
+FR_EXPORT int routed_sort_pairs(const int* ids, int rows, int top, int experts, int* offsets, int* pos, int* row_at, cudaStream_t stream) {
+    if (rows <= 0) return FR_OK;
+    if (experts < 1 || experts > 256) FR_REFUSE("sort_pairs: %d experts (1 to 256)", experts);
+    FR_CUDA(fr_launch(sort_pairs_kernel, dim3(1), dim3(1024), 0, stream, ids, rows * top, top, experts, offsets, pos, row_at));
+    FR_CHECK_LAUNCH("sort_pairs");
+    return FR_OK;
+}
+
+// out [rows][width] = residual + sum over a row's choices of weight * part[pos[pair]]
+FR_EXPORT int routed_combine(const float* part, const int* ids, const float* weights, const int* pos, const void* residual, void* out,
+                             int res_dtype, int rows, int top, int width, cudaStream_t stream) {
+    if (rows <= 0) return FR_OK;
+    const dim3 cg((width + 255) / 256, rows < 65535 ? rows : 65535);
+    if (res_dtype == FR_F32) FR_CUDA(fr_launch(combine_kernel<float>, cg, dim3(256), 0, stream, part, ids, weights, pos, (const float*)residual,
+                                               (float*)out, rows, top, width));
+    else if (res_dtype == FR_BF16) FR_CUDA(fr_launch(combine_kernel<bf16>, cg, dim3(256), 0, stream, part, ids, weights, pos,
+                                                     (const bf16*)residual, (bf16*)out, rows, top, width));
+    else FR_REFUSE("combine: unknown residual dtype %d", res_dtype);
+    FR_CHECK_LAUNCH("combine");
     return FR_OK;
 }

@@ -160,6 +160,12 @@ public:
     void scale_by_route(Tensor& act, const Tensor& dense, int experts, int inner);
     Tensor expert_gate_up(const Tensor& h, const Routing& r, const Tensor& w_gate_up, int top, int inner);
     Tensor expert_down_combine(const Tensor& act, const Routing& r, const Tensor& w_down, const Tensor& residual, int top, int inner);
+    // Many rows: the rows are gathered expert by expert and every expert with rows runs its two products on the tensor
+    // cores over its own rows only.  The host reads the experts' row counts (one small copy and a wait per call), so this
+    // is for prompts, never inside a captured step.  w_gate_up [experts * 2 * inner, width] (gate and up row by row in
+    // turn), w_down [width, experts * inner].
+    Tensor experts_grouped(const Tensor& h, const Routing& r, const Tensor& w_gate_up, const Tensor& w_down, const Tensor& residual,
+                           int top, int inner);
 
     // ---- matrix products: x [rows, k] @ weight [n, k]^T (+ bias [n]) (+ residual [rows, n])
     Tensor linear(const Rows& x, const Tensor& weight, const Tensor* bias = nullptr, const Tensor* residual = nullptr,

@@ -111,7 +111,8 @@ FAMILY(Recurrence, recurrence, "recurrence", resolve(h, fam, "recurrence_shift_m
 FAMILY(Routed, routed, "routed", resolve(h, fam, "routed_route", t.route);
        resolve(h, fam, "routed_scale_by_route", t.scale_by_route); resolve(h, fam, "routed_gate_up", t.gate_up);
        resolve(h, fam, "routed_down_combine", t.down_combine);
-       resolve(h, fam, "routed_down_scratch_floats", t.down_scratch_floats);)
+       resolve(h, fam, "routed_down_scratch_floats", t.down_scratch_floats);
+       resolve(h, fam, "routed_sort_pairs", t.sort_pairs); resolve(h, fam, "routed_combine", t.combine);)
 FAMILY(AttentionMma, attention_mma, "attention_mma", resolve(h, fam, "attention_mma", t.run);
        resolve(h, fam, "attention_mma_clusters_at_once", t.clusters_at_once);)
 FAMILY(AttentionTc, attention_tc, "attention_tc", resolve(h, fam, "attention_tc", t.run);)

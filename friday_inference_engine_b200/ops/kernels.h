@@ -86,6 +86,8 @@ struct Routed {
     int (*down_combine)(const void*, const int*, const float*, const void*, int, const void*, void*, int, int, int, int, int, int,
                         float*, int, cudaStream_t);
     long long (*down_scratch_floats)(int, int, int, int, int);
+    int (*sort_pairs)(const int*, int, int, int, int*, int*, int*, cudaStream_t);
+    int (*combine)(const float*, const int*, const float*, const int*, const void*, void*, int, int, int, int, cudaStream_t);
 };
 struct AttentionMma {
     last_error_fn last_error;

@@ -395,6 +395,40 @@ Tensor Ops::expert_down_combine(const Tensor& act, const Routing& r, const Tenso
     return out;
 }
 
+Tensor Ops::experts_grouped(const Tensor& h, const Routing& r, const Tensor& w_gate_up, const Tensor& w_down, const Tensor& residual,
+                            int top, int inner) {
+    const int64_t rows = h.rows(), width = h.cols(), n_pairs = rows * top;
+    const int experts = (int)(w_gate_up.rows() / (2 * (int64_t)inner));
+    const auto& k = kernels::routed();
+    int* offsets = (int*)arena->alloc((size_t)(experts + 1) * sizeof(int));
+    int* pos = (int*)arena->alloc((size_t)n_pairs * sizeof(int));
+    int* row_at = (int*)arena->alloc((size_t)n_pairs * sizeof(int));
+    {
+        Timed t(*this, Other);
+        call(launches_, k, k.sort_pairs((const int*)r.ids.data, (int)rows, top, experts, offsets, pos, row_at, stream_), "sort_pairs");
+    }
+    std::vector<int> off((size_t)experts + 1);
+    cuda_check(cudaMemcpyAsync(off.data(), offsets, off.size() * sizeof(int), cudaMemcpyDeviceToHost, stream_), "cudaMemcpyAsync");
+    cuda_check(cudaStreamSynchronize(stream_), "cudaStreamSynchronize");
+    Tensor gathered = gather_rows(row_at, n_pairs, h);
+    Tensor part = alloc(DType::F32, n_pairs, width);
+    for (int e = 0; e < experts; ++e) {
+        const int64_t lo = off[(size_t)e], n = off[(size_t)e + 1] - lo;
+        if (n <= 0) continue;
+        Tensor act = linear_swiglu(Rows(gathered.row_slice(lo, n)), w_gate_up.row_slice((int64_t)e * 2 * inner, 2 * (int64_t)inner));
+        Tensor wd = w_down;                          // this expert's columns, the matrix's row stride
+        wd.data = (char*)w_down.data + (size_t)e * inner * dtype_size(w_down.dtype);
+        wd.shape[1] = inner;
+        Tensor out = part.row_slice(lo, n);
+        linear(Rows(act), wd, nullptr, nullptr, (int)DType::F32, &out);
+    }
+    Tensor result = alloc(residual.dtype, residual.rows(), residual.cols());
+    Timed t(*this, Other);
+    call(launches_, k, k.combine((const float*)part.data, (const int*)r.ids.data, (const float*)r.weights.data, pos, residual.data,
+                                 result.data, code(residual.dtype), (int)rows, top, (int)width, stream_), "combine");
+    return result;
+}
+
 // ------------------------------------------------------------------ matrix products
 bool Ops::tensor_core_ok(const Tensor& x, const Tensor& weight, const Tensor& out, const Tensor* residual) const {
     (void)residual;

@@ -14,6 +14,9 @@
 // router logits, the choice and the weights are fp32 (csrc/routed.cu).  Every part adds into the residual stream that it
 // is given, in that stream's dtype (32-bit floats for a model that keeps its stream so).
 #include <math.h>
+#include <stdlib.h>
+
+#include <string>
 
 #include "friday/ops.h"
 #include "friday/parts.h"
@@ -210,9 +213,11 @@ private:
 // (or over all of them with "softmax_all").  Expert e: Wd_e (silu(Wg_e h) * (Wu_e h)).  The experts' gate and up matrices
 // are kept stacked row by row in turn, expert after expert, and their down matrices side by side, so that
 //   few rows:   only the chosen experts' weights are read, once per (row, choice);
-//   many rows:  ALL experts run as one gated product on the tensor cores, the result is multiplied by the routing
-//               weight (zero for an expert that was not chosen) and one product over the down matrices side by side
-//               sums the chosen experts: experts / top times the arithmetic, but none of it on CUDA cores.
+//   many rows:  either the rows are gathered expert by expert and every expert runs its two products over its own rows
+//               (prompts; the host reads the row counts), or ALL experts run as one gated product on the tensor cores,
+//               the result is multiplied by the routing weight (zero for an expert that was not chosen) and one product
+//               over the down matrices side by side sums the chosen experts: experts / top times the arithmetic in two
+//               launches.  Whichever is estimated to be less work runs.
 class RoutedExperts : public FeedForward {
 public:
     RoutedExperts(const PartSpec& s, const BuildEnv& e) : FeedForward(e) {
@@ -234,11 +239,27 @@ public:
             declare(p + "down", {w, (int64_t)inner_}).stack_columns("w_down", (int64_t)x * inner_);
         }
     }
-    PartOut forward(Ops& ops, const Rows& h, const Tensor& residual, const StepContext&, Norm*) override {
+    PartOut forward(Ops& ops, const Rows& h, const Tensor& residual, const StepContext& ctx, Norm*) override {
         Tensor x = ops.materialize(h);
         Tensor logits = ops.linear(Rows(x), tensor("router"), &tensor("router.b"), nullptr, (int)DType::F32);
-        const bool dense = x.dtype == DType::BF16 && x.rows() > 32 && experts_ <= 16 * top_ && tensor("w_gate_up").dtype == DType::BF16;
+        const bool tensor_cores = x.dtype == DType::BF16 && x.rows() > 32 && tensor("w_gate_up").dtype == DType::BF16 &&
+                                  x.cols() % 8 == 0 && inner_ % 8 == 0;
+        // Arithmetic of the dense form against the grouped one, in units of a product's multiply-adds: all experts for
+        // every row, or the chosen ones plus what two launches per expert and the host's wait cost (measured on a B200:
+        // grouping broke even at width 2,048 with 8 experts of inner size 2,048, 2 chosen, 2,048 rows, and won a fifth
+        // of the prompt's time at width 4,096; a launch counts as 25 G multiply-adds, the wait as 100 G).  Grouping
+        // needs the host, so a one-token step (which may be captured in a graph) never groups.
+        const double per_row = 3.0 * (double)inner_ * (double)x.cols();
+        const double dense_work = (double)x.rows() * experts_ * per_row;
+        const double grouped_work = (double)x.rows() * top_ * per_row + (2.0 * experts_ * 25e9 + 100e9) / 2.0;
+        // FRIDAY_EXPERTS=grouped|dense|pairs forces a form where it can run (for comparisons and tests)
+        const char* force = getenv("FRIDAY_EXPERTS");
+        const std::string forced = force ? force : "";
+        const bool may_group = tensor_cores && !ctx.decode && ctx.rows == (int)x.rows() && ctx.n_seqs > 0;
+        const bool grouped = may_group && (forced == "grouped" || (forced.empty() && grouped_work < dense_work));
+        const bool dense = tensor_cores && !grouped && (forced == "dense" || (forced.empty() && experts_ <= 16 * top_));
         Ops::Routing r = ops.route(logits, top_, softmax_all_, dense);
+        if (grouped) return PartOut(ops.experts_grouped(x, r, tensor("w_gate_up"), tensor("w_down"), residual, top_, inner_));
         if (dense) {
             Tensor act = ops.linear_swiglu(Rows(x), tensor("w_gate_up"));
             ops.scale_by_route(act, r.dense, experts_, inner_);

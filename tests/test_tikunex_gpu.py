@@ -70,6 +70,17 @@ CONFIGS = {
         {"type": "parallel", "mixer": par(4, 2, 32, 64, 130, 70, 0.18, 2, 32, 16, 1.1, 0.9), "mlp": moe(8, 2, 64)},
         {"type": "gla", "mixer": gla(4, 32, 16, 16.0, 8), "mlp": None},
     ], loop=(1, 3, 2), side=16),
+    # sizes that fit no tile: a width that is no multiple of 8 (no tensor-core product at all), head sizes of 24 and 40,
+    # inner sizes of 6 and 56, more kept tokens than the window is long, three passes of the loop
+    "W": config(100, 333, [
+        {"type": "parallel", "mixer": par(6, 3, 24, 40, 50, 70, 0.2, 2, 24, 6, 0.9, 1.1), "mlp": moe(3, 2, 56)},
+        {"type": "gla", "mixer": gla(2, 24, 40, 3.0, 6), "mlp": moe(3, 1, 56)},
+    ], loop=(0, 2, 3), side=6),
+    # the same head sizes on a width that the tensor cores take; so many experts that prompts, too, run them per (row, choice)
+    "V": config(192, 333, [
+        {"type": "gla", "mixer": gla(2, 24, 40, 3.0, 6), "mlp": moe(40, 2, 24)},
+        {"type": "parallel", "mixer": par(6, 3, 24, 40, 50, 70, 0.2, 2, 24, 6, 0.9, 1.1), "mlp": moe(40, 2, 24)},
+    ], side=6),
     # single mechanisms
     "gla_only": config(64, 100, [{"type": "gla", "mixer": gla(2, 16, 24, 2.0, 4), "mlp": None}]),
     "parallel_only": config(64, 100, [{"type": "parallel", "mixer": par(4, 2, 16, 8, 12, 2, 0.4, 2, 16, 4, 1.2, 0.8), "mlp": None}]),
@@ -191,7 +202,7 @@ def test_each_mechanism_alone(root, name, dtype):
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
-@pytest.mark.parametrize("name,n", [("X", 150), ("Y", 70), ("Z", 300)])
+@pytest.mark.parametrize("name,n", [("X", 150), ("Y", 70), ("Z", 300), ("W", 200), ("V", 200)])
 def test_whole_prompt(root, name, n, dtype):
     eng, cfg, _ = engine(root, name, dtype)
     (p,) = prompts([n], cfg["vocab"], 5)
@@ -200,6 +211,24 @@ def test_whole_prompt(root, name, n, dtype):
     eng.free_slot(s)
     agree(got, root, name, p, list(range(n)), dtype, "%s whole %d" % (name, n))
     assert nothing_held(eng)
+
+
+@pytest.mark.parametrize("form", ["grouped", "dense", "pairs"])
+@pytest.mark.parametrize("name", ["Z", "V"])
+def test_every_form_of_the_experts(root, name, form, monkeypatch):
+    """The three ways in which routed experts run for many rows in bfloat16 (rows gathered by expert, all experts
+    with zero weights for the unchosen, one block per row and choice) agree with the plain implementation."""
+    monkeypatch.setenv("FRIDAY_EXPERTS", form)
+    eng, cfg, _ = engine(root, name, "bfloat16")
+    lengths = [150, 3, 70]
+    ps = prompts(lengths, cfg["vocab"], 21)
+    slots = [eng.alloc_slot() for _ in ps]
+    got = eng.step(slots, ps, [list(range(n)) for n in lengths], to="host")
+    at = 0
+    for s, p, n in zip(slots, ps, lengths):
+        eng.free_slot(s)
+        agree(got[at:at + n], root, name, p, list(range(n)), "bfloat16", "%s experts %s, %d tokens" % (name, form, n))
+        at += n
 
 
 def test_the_window_and_the_kept_tokens_show(root):
@@ -217,12 +246,12 @@ def test_the_window_and_the_kept_tokens_show(root):
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
-@pytest.mark.parametrize("name", ["X", "Z"])
+@pytest.mark.parametrize("name", ["X", "Z", "W", "V"])
 def test_prompt_then_token_by_token(root, name, dtype):
     """The last tokens one by one: the window passes over decoded tokens, pages fill and are given back, the kept
     first tokens stay."""
     eng, cfg, _ = engine(root, name, dtype)
-    n, tail = (120, 60) if name == "X" else (330, 150)
+    n, tail = (330, 150) if name == "Z" else (120, 60)
     (p,) = prompts([n], cfg["vocab"], 6)
     s = eng.alloc_slot()
     got = [eng.step([s], [p[:n - tail]], [[n - tail - 1]], to="host")]
@@ -245,7 +274,7 @@ def test_all_tokens_one_by_one(root, dtype):
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
-@pytest.mark.parametrize("name,cuts", [("X", [2, 3, 7, 64, 65, 9]), ("Z", [64, 2, 128, 100, 6]), ("Y", [1, 2, 30, 37])])
+@pytest.mark.parametrize("name,cuts", [("X", [2, 3, 7, 64, 65, 9]), ("Z", [64, 2, 128, 100, 6]), ("Y", [1, 2, 30, 37]), ("W", [5, 64, 3, 70])])
 def test_portions(root, name, cuts, dtype):
     """A prompt cut into steps of several sizes, down to two tokens (and one)."""
     eng, cfg, _ = engine(root, name, dtype)

@@ -547,7 +547,7 @@ def tikunex_config(width, layers=4, vocab=32768, window=1024, experts=8, top=2):
     """A Tikunex configuration whose layers have sizes like a real model's of this width: gated linear attention with
     keys of half and values of the full width; windowed attention (keys of 64, values of 128) beside shift-decay mixing
     with heads of 64; `experts` experts of inner size `width`, `top` chosen; the last three layers run twice."""
-    gla = {"heads": width // 128, "dim": 64, "vdim": 128, "tau": 16.0, "decay_rank": 64}
+    gla = {"heads": width // 128, "dim": 64, "vdim": 128, "tau": 8.0, "decay_rank": 64}
     par = {"left": {"heads": width // 128, "kv_heads": max(1, width // 512), "dim": 64, "vdim": 128, "scale": 0.125,
                     "mask": {"size": window, "keep_first": 4}},
            "right": {"heads": width // 64, "dim": 64, "decay_rank": 64}, "left_scale": 1.0, "right_scale": 1.0}

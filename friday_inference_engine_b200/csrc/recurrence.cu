@@ -125,6 +125,7 @@ __global__ void scan_kernel(ScanArgs p) {
     float* sa = sk + SCAN_TOKENS * DK;
     float* su = sa + SCAN_TOKENS * DK;                // [DK] bonus
     float* sd = su + DK;                              // [DK] product of the decays (PHASE 1)
+    float* sv = sd + DK;                              // [SCAN_TOKENS][threads] each thread's value channel
     const int seq = PHASE == 0 ? blockIdx.x : blockIdx.x / p.max_segs, seg = PHASE == 0 ? 0 : blockIdx.x % p.max_segs;
     const int head = blockIdx.y;
     const int col = blockIdx.z * p.cols + threadIdx.x;
@@ -166,6 +167,11 @@ __global__ void scan_kernel(ScanArgs p) {
             sk[idx] = kv;
             sa[idx] = av;
         }
+        // this thread's value channel of the staged tokens: loaded together, ahead of the chain that uses them
+#pragma unroll
+        for (int t = 0; t < SCAN_TOKENS; ++t)
+            if (live_col && t < nt)
+                sv[t * blockDim.x + threadIdx.x] = fr_load((const T*)p.v + (size_t)(r0 + t0 + t) * p.ld_v + head * p.dv + col);
         __syncthreads();
         if (PHASE == 1 && blockIdx.z == 0)
             for (int i = threadIdx.x; i < p.dk; i += blockDim.x) {
@@ -176,7 +182,7 @@ __global__ void scan_kernel(ScanArgs p) {
         if (live_col) {
             for (int t = 0; t < nt; ++t) {
                 const size_t row = (size_t)(r0 + t0 + t);
-                const float vv = fr_load((const T*)p.v + row * p.ld_v + head * p.dv + col);
+                const float vv = sv[t * blockDim.x + threadIdx.x];
                 const float4* q4 = (const float4*)(sq + t * DK);
                 const float4* k4 = (const float4*)(sk + t * DK);
                 const float4* a4 = (const float4*)(sa + t * DK);
@@ -305,7 +311,7 @@ __global__ void __launch_bounds__(128) head_norm_gate_kernel(NormGateArgs p) {
 
 template <typename T, int DK>
 int launch_scan(const ScanArgs& p, int n_seqs, int splits, int threads, cudaStream_t stream) {
-    const size_t smem = (size_t)(3 * SCAN_TOKENS + 2) * DK * sizeof(float);
+    const size_t smem = ((size_t)(3 * SCAN_TOKENS + 2) * DK + (size_t)SCAN_TOKENS * threads) * sizeof(float);
     if (p.seg_len <= 0) {
         FR_CUDA(fr_launch(scan_kernel<T, DK, 0>, dim3(n_seqs, p.heads, splits), dim3(threads), smem, stream, p));
         FR_CHECK_LAUNCH("scan");

@@ -68,7 +68,7 @@ CONFIGS = {
     "Z": config(128, 512, [
         {"type": "gla", "mixer": gla(2, 64, 64, 8.0, 16), "mlp": moe(8, 2, 64)},
         {"type": "parallel", "mixer": par(4, 2, 32, 64, 130, 70, 0.18, 2, 32, 16, 1.1, 0.9), "mlp": moe(8, 2, 64)},
-        {"type": "gla", "mixer": gla(4, 32, 16, 16.0, 8), "mlp": None},
+        {"type": "gla", "mixer": gla(4, 32, 16, 12.0, 8), "mlp": None},
     ], loop=(1, 3, 2), side=16),
     # sizes that fit no tile: a width that is no multiple of 8 (no tensor-core product at all), head sizes of 24 and 40,
     # inner sizes of 6 and 56, more kept tokens than the window is long, three passes of the loop

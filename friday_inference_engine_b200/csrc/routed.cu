@@ -416,6 +416,18 @@ down_combine_kernel(const T* __restrict__ act, const int* __restrict__ ids, cons
     }
 }
 
+// Channels (of the inner size, or of the width) that a block of the by-expert kernels owns; FRIDAY_EXPERT_TILE overrides
+// (a multiple of 8, for measurements: 8 to 64 differ by less than a tenth).
+inline int expert_tile() {
+    static int v = 0;
+    if (v == 0) {
+        const char* e = getenv("FRIDAY_EXPERT_TILE");
+        const int t = e ? atoi(e) : 0;
+        v = (t >= 8 && t <= 256 && t % 8 == 0) ? t : 16;
+    }
+    return v;
+}
+
 }  // namespace
 
 FR_EXPORT int routed_route(const float* logits, int ld, int rows, int experts, int top, int softmax_all, int* ids, float* weights,
@@ -456,7 +468,7 @@ FR_EXPORT int routed_gate_up(const void* h, const int* ids, const void* w_gate_u
     const size_t share = (size_t)(rows < MAX_SHARE ? rows : MAX_SHARE) * width * esize;     // rows that can choose one expert
     if (dtype == FR_BF16 && rows <= MAX_SHARE && experts > 0 && width % (16 / esize) == 0 && share <= 160 * 1024 &&
         ((((uintptr_t)h) | ((uintptr_t)w_gate_up)) & 15) == 0) {
-        const int eper = 16;                     // 16 inner channels per block: enough blocks to fill the device
+        const int eper = expert_tile();          // inner channels per block: enough blocks to fill the device
         const dim3 eg(experts, (inner + eper - 1) / eper);
         if (dtype == FR_F32) {
             if (share > 48 * 1024) FR_CUDA(cudaFuncSetAttribute(gate_up_by_expert_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)share));
@@ -502,7 +514,7 @@ FR_EXPORT int routed_down_combine(const void* act, const int* ids, const float* 
     if (scratch != nullptr && routed_down_scratch_floats(rows, top, width, inner, dtype) > 0 && experts > 0 && ld_down % 8 == 0 &&
         ((((uintptr_t)act) | ((uintptr_t)w_down)) & 15) == 0 && rows <= 65535) {
         const size_t share = (size_t)(rows < MAX_SHARE ? rows : MAX_SHARE) * inner * 2;
-        const int per = 16;
+        const int per = expert_tile();
         if (share > 48 * 1024) FR_CUDA(cudaFuncSetAttribute(down_by_expert_kernel<bf16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)share));
         FR_CUDA(fr_launch(down_by_expert_kernel<bf16>, dim3(experts, (width + per - 1) / per), dim3(256), share, stream, (const bf16*)act, ids,
                           (const bf16*)w_down, ld_down, scratch, rows, top, width, inner, per));

@@ -257,12 +257,22 @@ __global__ void __launch_bounds__(256) scan_combine_kernel(ScanArgs p, int carry
     for (int e = blockIdx.z * blockDim.x + threadIdx.x; e < per; e += gridDim.z * blockDim.x) {
         const int i = e / p.dv;
         float r = S[e];
-        for (int sg = 0; sg < segs; ++sg) {
-            const size_t at = ((size_t)seq * p.max_segs + sg) * p.heads + head;
-            float* U = p.seg_u + at * per;
-            const float u = U[e];
-            U[e] = r;
-            r = fmaf(p.seg_d[at * p.dk + i], r, u);
+        for (int s0 = 0; s0 < segs; s0 += 8) {              // eight segments' numbers are loaded together, then chained
+            float u[8], d[8];
+#pragma unroll
+            for (int k = 0; k < 8; ++k) {
+                const size_t at = ((size_t)seq * p.max_segs + min(s0 + k, segs - 1)) * p.heads + head;
+                u[k] = p.seg_u[at * per + e];
+                d[k] = p.seg_d[at * p.dk + i];
+            }
+#pragma unroll
+            for (int k = 0; k < 8; ++k) {
+                if (s0 + k < segs) {
+                    const size_t at = ((size_t)seq * p.max_segs + s0 + k) * p.heads + head;
+                    p.seg_u[at * per + e] = r;
+                    r = fmaf(d[k], r, u[k]);
+                }
+            }
         }
         S[e] = r;
     }
@@ -375,10 +385,12 @@ FR_EXPORT int recurrence_scan_plan(int n_seqs, int max_q_len, int heads, int dk,
     *scratch_floats = 0;
     if (max_q_len < 128) return 0;
     const int sms = fr_sm_count() > 0 ? fr_sm_count() : 128;
-    // enough blocks for two waves of 32-channel blocks, segments of 32 tokens at least and 256 at most
+    // The chain of a segment waits on memory between its staged tokens, and only other warps hide that: a profile of
+    // 7 warps per SM showed them stalled on loads three cycles of four.  So the segments are made short enough for
+    // some 24 warps per SM (a warp owns 32 value channels of one head), 32 tokens at least and 256 at most.
     const long long base = (long long)n_seqs * heads * ((dv + 31) / 32);
     int seg = 256;
-    while (seg > 32 && base * ((max_q_len + seg - 1) / seg) < 4LL * sms) seg >>= 1;
+    while (seg > 32 && base * ((max_q_len + seg - 1) / seg) < 24LL * sms) seg >>= 1;
     const long long segs = (max_q_len + seg - 1) / seg;
     if (segs < 2) return 0;
     *scratch_floats = (long long)n_seqs * segs * heads * ((long long)dk * dv + dk);

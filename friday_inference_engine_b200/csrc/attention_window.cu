@@ -56,7 +56,7 @@ __device__ __forceinline__ void split2(float x, float y, uint32_t& hi, uint32_t&
 }
 
 template <int DK, int DV>
-__global__ void __launch_bounds__(128) window_prefill_kernel(WinArgs p) {
+__global__ void __launch_bounds__(128, 3) window_prefill_kernel(WinArgs p) {
     extern __shared__ __align__(16) unsigned char smem_raw[];
     bf16* sq = (bf16*)smem_raw;                           // [BM][DK + PAD]
     bf16* sk = sq + BM * (DK + PAD);                      // [BN][DK + PAD]
@@ -132,7 +132,10 @@ __global__ void __launch_bounds__(128) window_prefill_kernel(WinArgs p) {
         }
         const bf16* vp = p.v_pool + ((size_t)page * BN * p.nkv + kvh) * p.dv;
         for (int idx = tid; idx < BN * (DV / 8); idx += 128) {
-            const int r = idx % BN, c = (idx / BN) * 8;      // consecutive threads: consecutive keys of one piece of 8 channels
+            // consecutive threads take consecutive keys of one piece of 8 channels: the transposed 2-byte stores below then
+            // fall into different banks (consecutive pieces of one key's row, which would read memory in longer runs, put
+            // sixteen threads on one bank and made the kernel a third slower)
+            const int r = idx % BN, c = (idx / BN) * 8;
             const bf16* src = vp + (size_t)r * p.nkv * p.dv + c;
             uint4 v = make_uint4(0, 0, 0, 0);
             if (b * BN + r <= last_pos) {

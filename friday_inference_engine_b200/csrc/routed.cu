@@ -470,17 +470,9 @@ FR_EXPORT int routed_gate_up(const void* h, const int* ids, const void* w_gate_u
         ((((uintptr_t)h) | ((uintptr_t)w_gate_up)) & 15) == 0) {
         const int eper = expert_tile();          // inner channels per block: enough blocks to fill the device
         const dim3 eg(experts, (inner + eper - 1) / eper);
-        if (dtype == FR_F32) {
-            if (share > 48 * 1024) FR_CUDA(cudaFuncSetAttribute(gate_up_by_expert_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)share));
-            FR_CUDA(fr_launch(gate_up_by_expert_kernel<float>, eg, dim3(256), share, stream, (const float*)h, ids, (const float*)w_gate_up,
-                              (float*)act, rows, top, width, inner, eper));
-        } else if (dtype == FR_BF16) {
-            if (share > 48 * 1024) FR_CUDA(cudaFuncSetAttribute(gate_up_by_expert_kernel<bf16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)share));
-            FR_CUDA(fr_launch(gate_up_by_expert_kernel<bf16>, eg, dim3(256), share, stream, (const bf16*)h, ids, (const bf16*)w_gate_up,
-                              (bf16*)act, rows, top, width, inner, eper));
-        } else {
-            FR_REFUSE("gate_up: unknown dtype %d", dtype);
-        }
+        if (share > 48 * 1024) FR_CUDA(cudaFuncSetAttribute(gate_up_by_expert_kernel<bf16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)share));
+        FR_CUDA(fr_launch(gate_up_by_expert_kernel<bf16>, eg, dim3(256), share, stream, (const bf16*)h, ids, (const bf16*)w_gate_up,
+                          (bf16*)act, rows, top, width, inner, eper));
         FR_CHECK_LAUNCH("gate_up (by expert)");
         return FR_OK;
     }

@@ -1,0 +1,359 @@
+// The delta rule: a mixer whose state per head is a matrix S [dk][dv] that every token first decays, then corrects
+// towards its value along its key, then reads with its query:
+//
+//     S <- diag(g_t) S            g_t one number per head, or one per head and key channel
+//     u_t = beta_t (v_t - S^T k_t)
+//     S <- S + k_t u_t^T
+//     o_t = S^T q_t               (the read sees the present token's write)
+//
+// and the kernels around it:
+//
+//   conv_prepare   q, k, v channels of the stacked projection pass a short causal convolution over time (taps per
+//                  channel, the last tap is the present token's; the taps-1 inputs before a step's first row come from
+//                  the sequence's state, zeros at a sequence's start), then silu; every q and k head is made a unit
+//                  vector x / sqrt(sum x^2 + unit_eps), q is multiplied by q_scale.  Results are fp32.
+//   conv_state     the last taps-1 inputs of every sequence become its state's history (after conv_prepare has read it)
+//   scan           the recurrence, per (sequence, head): a thread owns one value channel (a column of S, dk numbers in
+//                  registers), tokens are staged through shared memory eight at a time.  beta = sigmoid(raw),
+//                  g = exp(-exp(A_log) * softplus(raw + dt_bias)) are formed here in fp32.  Columns of S never mix, so
+//                  any split of the value channels over blocks is exact.
+//
+// State of a sequence: [taps-1][channels] history (channel order of the stacked projection: q, k, v), then the heads'
+// matrices [heads][dk][dv], all fp32.  Everything here is fp32 arithmetic; only the projection's rows may be bf16.
+#include <math.h>
+
+#include "common.cuh"
+
+FR_EXPORT const char* delta_last_error() { return fr_error_text; }
+
+typedef __nv_bfloat16 bf16;
+
+namespace {
+
+constexpr int MAX_TAPS = 8;
+
+struct ConvArgs {
+    const void* x;            // [rows][ld]: q channels at q_off, k at k_off, v at v_off
+    const void* taps_w;       // [channels][taps] in channel order q, k, v
+    int w_dtype;
+    float* out;               // [rows][channels] fp32
+    float* state;             // [slots][state_stride], history at offset 0
+    long long state_stride;
+    const int* row_seq;
+    const int* seq_start;
+    const int* seq_qlen;
+    const int* seq_slots;
+    int ld, q_off, k_off, v_off, qk_heads, dk, v_channels, taps, rows;
+    float q_scale, unit_eps;
+};
+
+__device__ __forceinline__ float silu_f(float z) { return z / (1.0f + expf(-z)); }
+
+// convolution + silu of channel c (index into q|k|v) at `row`, whose sequence starts at row r0 with history `hist`
+template <typename T>
+__device__ __forceinline__ float conv_at(const ConvArgs& p, const T* x, int src_col, int c, int row, int r0, const float* hist,
+                                         int channels) {
+    const FrVec w{p.taps_w, p.w_dtype};
+    float acc = 0.f;
+    for (int j = 0; j < p.taps; ++j) {
+        const int back = p.taps - 1 - j;                 // rows before the present one
+        const int r = row - back;
+        float in;
+        if (r >= r0) in = fr_load(x + (size_t)r * p.ld + src_col);
+        else in = hist[(size_t)(p.taps - 1 + (r - r0)) * channels + c];
+        acc = fmaf(w.at(c * p.taps + j), in, acc);
+    }
+    return silu_f(acc);
+}
+
+// One block per row.  Warps take the q and k heads in turn (a head's channels over the lanes, then the unit norm),
+// then all threads take the v channels.
+template <typename T>
+__global__ void __launch_bounds__(256) conv_prepare_kernel(ConvArgs p) {
+    fr_pdl_wait();
+    fr_pdl_launch();
+    const int row = blockIdx.x;
+    const int seq = p.row_seq[row];
+    if (seq < 0) return;
+    const int r0 = p.seq_start[seq];
+    const int qk = p.qk_heads * p.dk, channels = 2 * qk + p.v_channels;
+    const float* hist = p.state + (size_t)p.seq_slots[seq] * p.state_stride;
+    const T* x = (const T*)p.x;
+    float* out = p.out + (size_t)row * channels;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, warps = blockDim.x >> 5;
+    for (int item = warp; item < 2 * p.qk_heads; item += warps) {
+        const bool is_q = item < p.qk_heads;
+        const int head = is_q ? item : item - p.qk_heads;
+        const int c0 = item * p.dk;                                  // channel index in q|k|v order
+        const int src0 = (is_q ? p.q_off : p.k_off) + head * p.dk;
+        float vals[8];
+        float ss = 0.f;
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+            const int d = lane + 32 * i;
+            vals[i] = 0.f;
+            if (d < p.dk) {
+                vals[i] = conv_at(p, x, src0 + d, c0 + d, row, r0, hist, channels);
+                ss = fmaf(vals[i], vals[i], ss);
+            }
+        }
+        ss = fr_warp_sum(ss);
+        const float inv = (is_q ? p.q_scale : 1.0f) / sqrtf(ss + p.unit_eps);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+            const int d = lane + 32 * i;
+            if (d < p.dk) out[c0 + d] = vals[i] * inv;
+        }
+    }
+    for (int d = threadIdx.x; d < p.v_channels; d += blockDim.x)
+        out[2 * qk + d] = conv_at(p, x, p.v_off + d, 2 * qk + d, row, r0, hist, channels);
+}
+
+// One block column per sequence: the history becomes the last taps-1 inputs of the sequence, this step's rows included.
+template <typename T>
+__global__ void __launch_bounds__(256) conv_state_kernel(ConvArgs p) {
+    fr_pdl_wait();
+    fr_pdl_launch();
+    const int seq = blockIdx.x;
+    const int r0 = p.seq_start[seq], n = p.seq_qlen[seq];
+    if (n <= 0 || p.row_seq[r0] < 0) return;
+    const int qk = p.qk_heads * p.dk, channels = 2 * qk + p.v_channels;
+    float* hist = p.state + (size_t)p.seq_slots[seq] * p.state_stride;
+    const T* x = (const T*)p.x;
+    const int keep = p.taps - 1;
+    for (int c = blockIdx.y * blockDim.x + threadIdx.x; c < channels; c += gridDim.y * blockDim.x) {
+        const int src = c < qk ? p.q_off + c : (c < 2 * qk ? p.k_off + (c - qk) : p.v_off + (c - 2 * qk));
+        float next[MAX_TAPS];
+#pragma unroll
+        for (int j = 0; j < MAX_TAPS; ++j) {
+            if (j < keep) {
+                const int idx = n - keep + j;            // row of the step, counted from the sequence's first row
+                next[j] = idx >= 0 ? fr_load(x + (size_t)(r0 + idx) * p.ld + src) : hist[(size_t)(j + n) * channels + c];
+            }
+        }
+#pragma unroll
+        for (int j = 0; j < MAX_TAPS; ++j)
+            if (j < keep) hist[(size_t)j * channels + c] = next[j];
+    }
+}
+
+struct ScanArgs {
+    const float* qkv;         // [rows][channels] from conv_prepare: q heads, k heads, v heads
+    const void* a_raw;        // [rows][ld_a]: per head, or per head and key channel (per_channel)
+    const void* b_raw;        // [rows][ld_b]: per head
+    int raw_dtype;
+    const void* a_log;        // [heads]
+    const void* dt_bias;      // [heads] or [heads * dk]
+    int vec_dtype;
+    float* out;               // [rows][heads * dv]
+    float* state;             // [slots][state_stride]; S of head h at s_off + h * dk * dv, laid out [dk][dv]
+    long long state_stride, s_off;
+    const int* row_seq;
+    const int* seq_start;
+    const int* seq_qlen;
+    const int* seq_slots;
+    int ld_a, ld_b, heads, qk_heads, dk, dv, cols, per_channel;
+};
+
+constexpr int SCAN_TOKENS = 8;
+
+__device__ __forceinline__ float softplus_f(float z) { return fmaxf(z, 0.f) + log1pf(expf(-fabsf(z))); }
+
+template <typename TR>
+__device__ __forceinline__ float raw_at(const void* p, size_t i) { return fr_load((const TR*)p + i); }
+
+template <typename TR, int DK, bool PER_CHANNEL>
+__global__ void delta_scan_kernel(ScanArgs p) {
+    extern __shared__ float sm[];
+    float* sq = sm;                                   // [SCAN_TOKENS][DK]
+    float* sk = sq + SCAN_TOKENS * DK;
+    float* sg = sk + SCAN_TOKENS * DK;                // [SCAN_TOKENS][DK] decays (per channel), or [SCAN_TOKENS] (per head)
+    float* sb = sg + (PER_CHANNEL ? SCAN_TOKENS * DK : SCAN_TOKENS);       // [SCAN_TOKENS] beta
+    float* sv = sb + SCAN_TOKENS;                     // [SCAN_TOKENS][threads]
+    const int seq = blockIdx.x, head = blockIdx.y;
+    const int col = blockIdx.z * p.cols + threadIdx.x;
+    const bool live_col = threadIdx.x < p.cols && col < p.dv;
+    const int r0 = p.seq_start[seq], n = p.seq_qlen[seq];
+    fr_pdl_wait();
+    fr_pdl_launch();
+    if (n <= 0 || p.row_seq[r0] < 0) return;
+    const int group = head / (p.heads / p.qk_heads);
+    const int qk = p.qk_heads * p.dk, channels = 2 * qk + p.heads * p.dv;
+    float* S = p.state + (size_t)p.seq_slots[seq] * p.state_stride + p.s_off + (size_t)head * p.dk * p.dv;
+    float s[DK];
+#pragma unroll
+    for (int i = 0; i < DK; ++i) s[i] = (live_col && i < p.dk) ? S[(size_t)i * p.dv + col] : 0.f;
+    const FrVec alog{p.a_log, p.vec_dtype}, dtb{p.dt_bias, p.vec_dtype};
+    const float rate = expf(alog.at(head));
+    for (int t0 = 0; t0 < n; t0 += SCAN_TOKENS) {
+        const int nt = min(SCAN_TOKENS, n - t0);
+        __syncthreads();
+        for (int idx = threadIdx.x; idx < nt * DK; idx += blockDim.x) {
+            const int t = idx / DK, i = idx - t * DK;
+            const size_t row = (size_t)(r0 + t0 + t);
+            float qv = 0.f, kv = 0.f, gv = 1.f;
+            if (i < p.dk) {
+                qv = p.qkv[row * channels + group * p.dk + i];
+                kv = p.qkv[row * channels + qk + group * p.dk + i];
+                if (PER_CHANNEL) {
+                    const float z = raw_at<TR>(p.a_raw, row * p.ld_a + head * p.dk + i) + dtb.at(head * p.dk + i);
+                    gv = expf(-rate * softplus_f(z));
+                }
+            }
+            sq[idx] = qv;
+            sk[idx] = kv;
+            if (PER_CHANNEL) sg[idx] = gv;
+        }
+        for (int t = threadIdx.x; t < nt; t += blockDim.x) {
+            const size_t row = (size_t)(r0 + t0 + t);
+            const float zb = raw_at<TR>(p.b_raw, row * p.ld_b + head);
+            sb[t] = 1.0f / (1.0f + expf(-zb));
+            if (!PER_CHANNEL) {
+                const float z = raw_at<TR>(p.a_raw, row * p.ld_a + head) + dtb.at(head);
+                sg[t] = expf(-rate * softplus_f(z));
+            }
+        }
+#pragma unroll
+        for (int t = 0; t < SCAN_TOKENS; ++t)
+            if (live_col && t < nt) sv[t * blockDim.x + threadIdx.x] = p.qkv[(size_t)(r0 + t0 + t) * channels + 2 * qk + head * p.dv + col];
+        __syncthreads();
+        if (live_col) {
+            for (int t = 0; t < nt; ++t) {
+                const float4* q4 = (const float4*)(sq + t * DK);
+                const float4* k4 = (const float4*)(sk + t * DK);
+                const float4* g4 = (const float4*)(sg + t * DK);
+                const float gh = PER_CHANNEL ? 1.f : sg[t];
+                // decay, and what the decayed state holds along the key: four chains
+                float r = 0.f, r1 = 0.f, r2 = 0.f, r3 = 0.f;
+#pragma unroll
+                for (int i = 0; i < DK / 4; ++i) {
+                    const float4 k = k4[i];
+                    if (PER_CHANNEL) {
+                        const float4 g = g4[i];
+                        s[4 * i] *= g.x; s[4 * i + 1] *= g.y; s[4 * i + 2] *= g.z; s[4 * i + 3] *= g.w;
+                    } else {
+                        s[4 * i] *= gh; s[4 * i + 1] *= gh; s[4 * i + 2] *= gh; s[4 * i + 3] *= gh;
+                    }
+                    r = fmaf(k.x, s[4 * i], r);
+                    r1 = fmaf(k.y, s[4 * i + 1], r1);
+                    r2 = fmaf(k.z, s[4 * i + 2], r2);
+                    r3 = fmaf(k.w, s[4 * i + 3], r3);
+                }
+                r = (r + r1) + (r2 + r3);
+                const float u = sb[t] * (sv[t * blockDim.x + threadIdx.x] - r);
+                float o = 0.f, o1 = 0.f, o2 = 0.f, o3 = 0.f;
+#pragma unroll
+                for (int i = 0; i < DK / 4; ++i) {
+                    const float4 k = k4[i], q = q4[i];
+                    s[4 * i] = fmaf(k.x, u, s[4 * i]);         o = fmaf(q.x, s[4 * i], o);
+                    s[4 * i + 1] = fmaf(k.y, u, s[4 * i + 1]); o1 = fmaf(q.y, s[4 * i + 1], o1);
+                    s[4 * i + 2] = fmaf(k.z, u, s[4 * i + 2]); o2 = fmaf(q.z, s[4 * i + 2], o2);
+                    s[4 * i + 3] = fmaf(k.w, u, s[4 * i + 3]); o3 = fmaf(q.w, s[4 * i + 3], o3);
+                }
+                p.out[(size_t)(r0 + t0 + t) * ((size_t)p.heads * p.dv) + head * p.dv + col] = (o + o1) + (o2 + o3);
+            }
+        }
+    }
+    if (live_col) {
+#pragma unroll
+        for (int i = 0; i < DK; ++i)
+            if (i < p.dk) S[(size_t)i * p.dv + col] = s[i];
+    }
+}
+
+template <typename TR, int DK>
+int launch_scan(const ScanArgs& p, int n_seqs, int splits, int threads, cudaStream_t stream) {
+    const size_t floats = (size_t)2 * SCAN_TOKENS * DK + (p.per_channel ? (size_t)SCAN_TOKENS * DK : SCAN_TOKENS) + SCAN_TOKENS +
+                          (size_t)SCAN_TOKENS * threads;
+    const size_t smem = floats * sizeof(float);
+    const dim3 grid(n_seqs, p.heads, splits);
+    if (p.per_channel) FR_CUDA(fr_launch(delta_scan_kernel<TR, DK, true>, grid, dim3(threads), smem, stream, p));
+    else FR_CUDA(fr_launch(delta_scan_kernel<TR, DK, false>, grid, dim3(threads), smem, stream, p));
+    FR_CHECK_LAUNCH("delta scan");
+    return FR_OK;
+}
+
+template <typename TR>
+int scan_by_size(const ScanArgs& p, int n_seqs, int splits, int threads, cudaStream_t stream) {
+    if (p.dk <= 16) return launch_scan<TR, 16>(p, n_seqs, splits, threads, stream);
+    if (p.dk <= 32) return launch_scan<TR, 32>(p, n_seqs, splits, threads, stream);
+    if (p.dk <= 64) return launch_scan<TR, 64>(p, n_seqs, splits, threads, stream);
+    if (p.dk <= 128) return launch_scan<TR, 128>(p, n_seqs, splits, threads, stream);
+    if (p.dk <= 256) return launch_scan<TR, 256>(p, n_seqs, splits, threads, stream);
+    FR_REFUSE("delta scan: %d key channels per head (at most 256)", p.dk);
+}
+
+int fill_conv(ConvArgs& p, const void* x, int ld, int q_off, int k_off, int v_off, const void* taps_w, int w_dtype, float* out,
+              float* state, long long state_stride, const int* row_seq, const int* seq_start, const int* seq_qlen,
+              const int* seq_slots, int rows, int qk_heads, int dk, int v_channels, int taps, float q_scale, float unit_eps) {
+    if (taps < 1 || taps > MAX_TAPS) FR_REFUSE("short convolution: %d taps (1 to %d)", taps, MAX_TAPS);
+    if (dk <= 0 || dk > 256 || qk_heads <= 0 || v_channels <= 0) FR_REFUSE("short convolution: %d heads of %d, %d value channels", qk_heads, dk, v_channels);
+    p.x = x; p.taps_w = taps_w; p.w_dtype = w_dtype; p.out = out; p.state = state; p.state_stride = state_stride;
+    p.row_seq = row_seq; p.seq_start = seq_start; p.seq_qlen = seq_qlen; p.seq_slots = seq_slots;
+    p.ld = ld; p.q_off = q_off; p.k_off = k_off; p.v_off = v_off; p.qk_heads = qk_heads; p.dk = dk; p.v_channels = v_channels;
+    p.taps = taps; p.rows = rows; p.q_scale = q_scale; p.unit_eps = unit_eps;
+    return FR_OK;
+}
+
+}  // namespace
+
+// q, k (qk_heads x dk each) and v (v_channels) of x [rows][ld] -> out [rows][2 qk_heads dk + v_channels] fp32.
+FR_EXPORT int delta_conv_prepare(const void* x, int ld, int q_off, int k_off, int v_off, const void* taps_w, int w_dtype, float* out,
+                                 const float* state, long long state_stride, const int* row_seq, const int* seq_start,
+                                 const int* seq_slots, int rows, int qk_heads, int dk, int v_channels, int taps, float q_scale,
+                                 float unit_eps, int dtype, cudaStream_t stream) {
+    if (rows <= 0) return FR_OK;
+    ConvArgs p;
+    const int rc = fill_conv(p, x, ld, q_off, k_off, v_off, taps_w, w_dtype, out, (float*)state, state_stride, row_seq, seq_start,
+                             nullptr, seq_slots, rows, qk_heads, dk, v_channels, taps, q_scale, unit_eps);
+    if (rc != FR_OK) return rc;
+    if (dtype == FR_F32) FR_CUDA(fr_launch(conv_prepare_kernel<float>, dim3(rows), dim3(256), 0, stream, p));
+    else if (dtype == FR_BF16) FR_CUDA(fr_launch(conv_prepare_kernel<bf16>, dim3(rows), dim3(256), 0, stream, p));
+    else FR_REFUSE("short convolution: unknown dtype %d", dtype);
+    FR_CHECK_LAUNCH("conv_prepare");
+    return FR_OK;
+}
+
+FR_EXPORT int delta_conv_state(const void* x, int ld, int q_off, int k_off, int v_off, float* state, long long state_stride,
+                               const int* row_seq, const int* seq_start, const int* seq_qlen, const int* seq_slots, int n_seqs,
+                               int qk_heads, int dk, int v_channels, int taps, int dtype, cudaStream_t stream) {
+    if (n_seqs <= 0 || taps <= 1) return FR_OK;
+    ConvArgs p;
+    const int rc = fill_conv(p, x, ld, q_off, k_off, v_off, nullptr, 0, nullptr, state, state_stride, row_seq, seq_start, seq_qlen,
+                             seq_slots, 0, qk_heads, dk, v_channels, taps, 1.f, 0.f);
+    if (rc != FR_OK) return rc;
+    const int channels = 2 * qk_heads * dk + v_channels;
+    const dim3 grid(n_seqs, (channels + 255) / 256);
+    if (dtype == FR_F32) FR_CUDA(fr_launch(conv_state_kernel<float>, grid, dim3(256), 0, stream, p));
+    else if (dtype == FR_BF16) FR_CUDA(fr_launch(conv_state_kernel<bf16>, grid, dim3(256), 0, stream, p));
+    else FR_REFUSE("short convolution: unknown dtype %d", dtype);
+    FR_CHECK_LAUNCH("conv_state");
+    return FR_OK;
+}
+
+// per_channel 0: a_raw [rows][>= heads], dt_bias [heads]; 1: a_raw [rows][>= heads * dk], dt_bias [heads * dk].
+// raw_dtype: dtype of a_raw and b_raw; vec_dtype: dtype of a_log and dt_bias.
+FR_EXPORT int delta_scan(const float* qkv, const void* a_raw, int ld_a, const void* b_raw, int ld_b, int raw_dtype, const void* a_log,
+                         const void* dt_bias, int vec_dtype, float* out, float* state, long long state_stride, long long s_off,
+                         const int* row_seq, const int* seq_start, const int* seq_qlen, const int* seq_slots, int n_seqs, int heads,
+                         int qk_heads, int dk, int dv, int per_channel, cudaStream_t stream) {
+    if (n_seqs <= 0) return FR_OK;
+    if (heads <= 0 || qk_heads <= 0 || heads % qk_heads || dk <= 0 || dv <= 0)
+        FR_REFUSE("delta scan: %d heads on %d query/key heads, dk %d, dv %d", heads, qk_heads, dk, dv);
+    ScanArgs p;
+    p.qkv = qkv; p.a_raw = a_raw; p.b_raw = b_raw; p.raw_dtype = raw_dtype; p.a_log = a_log; p.dt_bias = dt_bias; p.vec_dtype = vec_dtype;
+    p.out = out; p.state = state; p.state_stride = state_stride; p.s_off = s_off; p.row_seq = row_seq; p.seq_start = seq_start;
+    p.seq_qlen = seq_qlen; p.seq_slots = seq_slots; p.ld_a = ld_a; p.ld_b = ld_b; p.heads = heads; p.qk_heads = qk_heads; p.dk = dk;
+    p.dv = dv; p.per_channel = per_channel ? 1 : 0;
+    // value channels per block: 32 where the device would otherwise stay empty, up to 128
+    const int sms = fr_sm_count() > 0 ? fr_sm_count() : 128;
+    int cols = 128;
+    while (cols > 32 && (long long)n_seqs * heads * ((dv + cols - 1) / cols) < 2LL * sms) cols >>= 1;
+    if (cols > ((dv + 31) / 32) * 32) cols = ((dv + 31) / 32) * 32;
+    p.cols = cols;
+    const int splits = (dv + cols - 1) / cols;
+    const int threads = cols < 64 ? 64 : cols;
+    if (raw_dtype == FR_F32) return scan_by_size<float>(p, n_seqs, splits, threads, stream);
+    if (raw_dtype == FR_BF16) return scan_by_size<bf16>(p, n_seqs, splits, threads, stream);
+    FR_REFUSE("delta scan: unknown dtype %d", raw_dtype);
+}

@@ -11,7 +11,7 @@
 //                    a_t is formed here, in fp32, from the raw projection z_t (+ bias):
 //                        mode 0:  a = sigmoid(z)^(1/tau) = exp(-softplus(-z) / tau)
 //                        mode 1:  a = exp(-exp(z))
-//   head_norm_gate   o / sqrt(mean_head(o^2) + eps) * weight * silu(gate) * out_scale, per (row, head)
+//   head_norm_gate   o / sqrt(mean_head(o^2) + eps) * weight * act(gate) * out_scale, per (row, head); act is silu or sigmoid
 //
 // The state, the decays, their logarithms and exponentials, the outer products and the unit norms are fp32
 // whatever the activations' dtype; q, k, v and the gate come from products in the activation dtype.
@@ -293,6 +293,7 @@ struct NormGateArgs {
     const int* row_seq;
     int rows, heads, dv, ld_gate;
     float eps, out_scale;
+    int gate_act;             // 0: silu(gate), 1: sigmoid(gate)
 };
 
 template <typename T>
@@ -314,8 +315,9 @@ __global__ void __launch_bounds__(128) head_norm_gate_kernel(NormGateArgs p) {
     T* out = (T*)p.out + (size_t)row * p.heads * p.dv + (size_t)head * p.dv;
     for (int c = lane; c < p.dv; c += 32) {
         const float gv = fr_load(g + c);
-        const float silu = gv / (1.0f + expf(-gv));
-        fr_store(out + c, o[c] * inv * w.at(p.weight_per_head ? head * p.dv + c : c) * silu);
+        const float sg = 1.0f / (1.0f + expf(-gv));
+        const float act = p.gate_act == 1 ? sg : gv * sg;
+        fr_store(out + c, o[c] * inv * w.at(p.weight_per_head ? head * p.dv + c : c) * act);
     }
 }
 
@@ -439,9 +441,10 @@ FR_EXPORT int recurrence_scan(const void* q, int ld_q, const void* k, int ld_k, 
 
 FR_EXPORT int recurrence_head_norm_gate(const float* o, const void* gate, int ld_gate, void* out, const void* weight,
                                         int weight_dtype, int weight_per_head, const int* row_seq, int rows, int heads, int dv,
-                                        float eps, float out_scale, int dtype, cudaStream_t stream) {
+                                        float eps, float out_scale, int gate_act, int dtype, cudaStream_t stream) {
     if (rows <= 0) return FR_OK;
     NormGateArgs p;
+    p.gate_act = gate_act;
     p.o = o; p.gate = gate; p.out = out; p.weight = weight; p.weight_dtype = weight_dtype; p.weight_per_head = weight_per_head;
     p.row_seq = row_seq; p.rows = rows; p.heads = heads; p.dv = dv; p.ld_gate = ld_gate; p.eps = eps; p.out_scale = out_scale;
     const int blocks = (rows * heads + 3) / 4;

@@ -90,6 +90,46 @@ __global__ void kv_store_kernel(const T* __restrict__ src, int ld, int k_off, in
     for (int i = threadIdx.x; i < nkv * vd; i += blockDim.x) vd_[i] = s[v_off + i];
 }
 
+// y = (x - mean) / sqrt(var + eps) * w + b with var the mean of the squared deviations, one block per row; two passes over
+// the row, so that the variance is not a difference of large numbers.  x and y may differ in dtype.
+template <typename TI, typename TO>
+__global__ void __launch_bounds__(256)
+layernorm_cast_kernel(const TI* __restrict__ x, FrVec w, FrVec b, TO* __restrict__ y, int width, float eps) {
+    __shared__ float partial[32];
+    fr_pdl_wait();
+    fr_pdl_launch();
+    const TI* xr = x + (size_t)blockIdx.x * width;
+    TO* yr = y + (size_t)blockIdx.x * width;
+    float sum = 0.f;
+    for (int i = threadIdx.x; i < width; i += blockDim.x) sum += fr_load(xr + i);
+    const float mean = block_sum(sum, partial) / (float)width;
+    float ss = 0.f;
+    for (int i = threadIdx.x; i < width; i += blockDim.x) {
+        const float d = fr_load(xr + i) - mean;
+        ss = fmaf(d, d, ss);
+    }
+    ss = block_sum(ss, partial);
+    const float inv = 1.0f / sqrtf(ss / (float)width + eps);
+    for (int i = threadIdx.x; i < width; i += blockDim.x) {
+        float v = (fr_load(xr + i) - mean) * inv * w.at(i);
+        if (b.p != nullptr) v += b.at(i);
+        fr_store(yr + i, v);
+    }
+}
+
+// out[r] = table[tokens[r]] * scale as 32-bit rows (ids outside the table leave zeros)
+template <typename TW>
+__global__ void embed_rows_kernel(const int* __restrict__ tokens, const TW* __restrict__ table, float* __restrict__ out, int width,
+                                  int vocab, float scale) {
+    fr_pdl_wait();
+    fr_pdl_launch();
+    const int token = tokens[blockIdx.x];
+    float* o = out + (size_t)blockIdx.x * width;
+    const bool ok = token >= 0 && token < vocab;
+    const TW* t = table + (size_t)(ok ? token : 0) * width;
+    for (int i = threadIdx.x; i < width; i += blockDim.x) o[i] = ok ? fr_load(t + i) * scale : 0.f;
+}
+
 __device__ __forceinline__ float gelu_tanh(float z) {
     return 0.5f * z * (1.0f + tanhf(0.7978845608028654f * (z + 0.044715f * z * z * z)));
 }
@@ -319,5 +359,32 @@ FR_EXPORT int residual_rms_add(float* x, const float* y, const void* norm, int n
     if (rows <= 0) return FR_OK;
     FR_CUDA(fr_launch(rms_add_kernel, dim3(rows), dim3(256), 0, stream, x, y, FrVec{norm, norm_dtype}, width, eps));
     FR_CHECK_LAUNCH("rms_add");
+    return FR_OK;
+}
+
+// bias null: none.  The weight and the bias share a dtype.
+FR_EXPORT int residual_layernorm_cast(const void* x, int in_dtype, const void* w, const void* b, int w_dtype, void* y, int out_dtype,
+                                      int n_rows, int width, float eps, cudaStream_t stream) {
+    if (n_rows <= 0) return FR_OK;
+    FrVec wv{w, w_dtype}, bv{b, w_dtype};
+    const int key = in_dtype * 2 + out_dtype;
+    switch (key) {
+        case 0: FR_CUDA(fr_launch(layernorm_cast_kernel<float, float>, dim3(n_rows), dim3(256), 0, stream, (const float*)x, wv, bv, (float*)y, width, eps)); break;
+        case 1: FR_CUDA(fr_launch(layernorm_cast_kernel<float, bf16>, dim3(n_rows), dim3(256), 0, stream, (const float*)x, wv, bv, (bf16*)y, width, eps)); break;
+        case 2: FR_CUDA(fr_launch(layernorm_cast_kernel<bf16, float>, dim3(n_rows), dim3(256), 0, stream, (const bf16*)x, wv, bv, (float*)y, width, eps)); break;
+        case 3: FR_CUDA(fr_launch(layernorm_cast_kernel<bf16, bf16>, dim3(n_rows), dim3(256), 0, stream, (const bf16*)x, wv, bv, (bf16*)y, width, eps)); break;
+        default: FR_REFUSE("layernorm_cast: unknown dtypes %d -> %d", in_dtype, out_dtype);
+    }
+    FR_CHECK_LAUNCH("layernorm_cast");
+    return FR_OK;
+}
+
+FR_EXPORT int residual_embed_rows(const int* tokens, const void* table, int table_dtype, float* out, int n_rows, int width, int vocab,
+                                  float scale, cudaStream_t stream) {
+    if (n_rows <= 0) return FR_OK;
+    if (table_dtype == FR_F32) FR_CUDA(fr_launch(embed_rows_kernel<float>, dim3(n_rows), dim3(256), 0, stream, tokens, (const float*)table, out, width, vocab, scale));
+    else if (table_dtype == FR_BF16) FR_CUDA(fr_launch(embed_rows_kernel<bf16>, dim3(n_rows), dim3(256), 0, stream, tokens, (const bf16*)table, out, width, vocab, scale));
+    else FR_REFUSE("embed_rows: unknown dtype %d", table_dtype);
+    FR_CHECK_LAUNCH("embed_rows");
     return FR_OK;
 }

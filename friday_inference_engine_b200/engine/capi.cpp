@@ -253,6 +253,7 @@ FR_API int friday_describe_model(const char* config_json, const char** json) {
             e.set("cache", Json(c.cache));
             e.set("write", Json(c.write));
             e.set("inject", Json(c.inject));
+            e.set("add_input", Json(c.add_input));
             program.push(e);
         }
         out.set("program", program);

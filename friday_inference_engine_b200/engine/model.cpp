@@ -184,9 +184,14 @@ void DecoderModel::load(WeightSource& source, Ops& ops) {
 DecoderModel::RunOut DecoderModel::run(Ops& ops, const StepContext& ctx, const std::vector<CacheView>& views,
                                        bool with_final_norm, Arena* layer_arenas[2]) {
     Arena* outer = ops.arena;
-    Tensor x = ops.embedding(ctx.tokens, ctx.rows, embedding);
-    if (spec.embed_scale != 1.0) ops.scale_rows(x, (float)spec.embed_scale);
-    if (embed_norm) x = embed_norm->forward(ops, x);
+    Tensor x;
+    if (spec.residual_f32 && !embed_norm) {
+        x = ops.embed_rows(ctx.tokens, ctx.rows, embedding, (float)spec.embed_scale);      // no rounding between table and stream
+    } else {
+        x = ops.embedding(ctx.tokens, ctx.rows, embedding);
+        if (spec.embed_scale != 1.0) ops.scale_rows(x, (float)spec.embed_scale);
+        if (embed_norm) x = embed_norm->forward(ops, x);
+    }
     if (spec.residual_f32 && x.dtype != DType::F32)
         throw ConfigError("a model with a 32-bit residual stream needs an embedding norm (or a token table) that yields 32-bit rows");
     const Tensor x0 = x;                    // what injections feed back in; it lives in the caller's arena
@@ -207,6 +212,11 @@ DecoderModel::RunOut DecoderModel::run(Ops& ops, const StepContext& ctx, const s
             // x <- W [x; x0]: both halves in the activation dtype, the sum of products straight into the stream's dtype
             Tensor both = ops.concat_cast(x, x0, env.dtype);
             x = ops.linear(Rows(both), injections[(size_t)call.inject], nullptr, nullptr, (int)x.dtype);
+            has_normed = false;
+        }
+        if (call.add_input) {
+            if (x.dtype != DType::F32) throw ConfigError("adding the embedding's output back in needs a 32-bit residual stream");
+            x = ops.add_scaled(x, x0, 1.0f);
             has_normed = false;
         }
         Norm* then = nullptr;

@@ -124,6 +124,10 @@ public:
     // residual + alpha * (x weight^T + bias): in the product's epilogue where residual and result share a dtype and
     // alpha is 1; otherwise the product in 32-bit and add_scaled
     Tensor linear_residual(const Rows& x, const Tensor& weight, const Tensor* bias, const Tensor& residual, float alpha = 1.0f);
+    // y = (x - mean) / sqrt(variance + eps) * weight + bias (bias null: none), x and y in dtypes of their own
+    Tensor layernorm_to(const Tensor& x, const Tensor& weight, const Tensor* bias, float eps, DType out_dtype);
+    // table[token] * scale as 32-bit rows: the start of a 32-bit residual stream, without a rounding in between
+    Tensor embed_rows(const int* tokens, int64_t n, const Tensor& table, float scale);
     // keys [n_kv_heads][head_dim] at column k_off and values [n_kv_heads][v_head_dim] at column v_off of every row of
     // `src` go to the cache rows of (row_seq, row_pos)
     void kv_store(const Tensor& src, int64_t k_off, int64_t v_off, const CacheView& view, const StepContext& ctx);
@@ -149,8 +153,43 @@ public:
     Tensor state_scan(const Tensor& q, const Tensor& k, const Tensor& v, const Tensor& z, const ScanSpec& spec, const CacheView& view,
                       const StepContext& ctx);
     // o [rows, heads * dv] fp32 -> o / rms_head(o) * weight * silu(gate) * out_scale in `dtype`
+    // gate_sigmoid: the gate passes a sigmoid instead of silu
     Tensor head_norm_gate(const Tensor& o, const Tensor& gate, const Tensor& weight, bool weight_per_head, int heads, int dv,
-                          float eps, float out_scale, DType dtype, const StepContext& ctx);
+                          float eps, float out_scale, DType dtype, const StepContext& ctx, bool gate_sigmoid = false);
+
+    // ---- the delta rule (csrc/delta.cu): a state per head that every token decays, corrects along its key and reads
+    struct DeltaSpec {
+        int heads = 0, qk_heads = 0, dk = 0, dv = 0, taps = 1;
+        bool per_channel = false;       // a decay per head and key channel instead of one per head
+        float q_scale = 1.f, unit_eps = 1e-6f;
+        int64_t q_off = 0, k_off = 0, v_off = 0;        // columns of q, k, v in the stacked projection
+    };
+    // Short causal convolution + silu of the q, k, v channels of `proj` (history from the state), unit q and k heads:
+    // [rows, 2 qk_heads dk + heads dv] fp32.  Then the state's history takes this step's last inputs.
+    Tensor conv_silu_unit(const Tensor& proj, const Tensor& taps, const DeltaSpec& spec, const CacheView& view, const StepContext& ctx);
+    // a_raw [rows, heads (* dk)], b_raw [rows, heads] (their row strides are used; one dtype), a_log [heads],
+    // dt_bias [heads (* dk)]: beta = sigmoid(b_raw), decay = exp(-exp(a_log) * softplus(a_raw + dt_bias)); out [rows, heads * dv] fp32
+    Tensor delta_scan(const Tensor& qkv, const Tensor& a_raw, const Tensor& b_raw, const Tensor& a_log, const Tensor& dt_bias,
+                      const DeltaSpec& spec, const CacheView& view, const StepContext& ctx);
+
+    // ---- attention over a cached latent (csrc/attention_latent.cu)
+    struct LatentSpec {
+        int heads = 0, dim = 0, rot = 0, rank = 0, vdim = 0;
+        float scale = 1.f, eps = 1e-5f, rot_mult = 1.f;
+        const float* freq = nullptr;    // device: rot / 2 angular frequencies
+        int64_t q_off = 0, kv_off = 0, gate_off = -1;   // columns of the stacked projection: queries, [latent | key part], gates
+    };
+    // Interleaved rotary encoding in place: dims [first, first + dims) of each of `heads` heads (head_stride apart) of every row
+    void rotate_pairs(Tensor& x, const StepContext& ctx, const float* freq, float mult, int heads, int64_t head_stride, int64_t first, int dims);
+    // From a row of the stacked projection: [normed latent | rotated key part] in the activation dtype (what the cache keeps),
+    // and the rotated query parts in their places of qf [rows, heads * (rank + rot)] fp32
+    Tensor latent_prepare(const Tensor& proj, const Tensor& norm_w, const LatentSpec& spec, Tensor& qf, const StepContext& ctx);
+    // out[row][h][n] = sum_k x[row][x_off + h * x_stride + k] * W_h: weights [heads * k, n] (per_head_rows_k) or [heads * n, k];
+    // gate (null: none): the result is multiplied by sigmoid(gate[row][gate_off + h]); out: head h at h * out_stride
+    void head_linear(const Tensor& x, int64_t x_off, int64_t x_stride, const Tensor& w, bool per_head_rows_k, Tensor& out,
+                     int64_t out_stride, const Tensor* gate, int64_t gate_off, int heads, int k, int n, const StepContext& ctx);
+    // qf [rows, heads * (rank + rot)] fp32 against the cached [latent | key part] rows -> [rows, heads * rank] fp32
+    Tensor latent_attention(const Tensor& qf, const Tensor* sink, const LatentSpec& spec, const CacheView& view, const StepContext& ctx);
 
     // ---- routed experts (csrc/routed.cu)
     struct Routing {

@@ -69,6 +69,7 @@ struct LayerCall {
     int cache = -1;         // cache entry that the layer's mixer uses in this call; -1: none
     bool write = true;      // false: read an entry that an earlier call filled
     int inject = -1;        // index into ModelSpec::injections of what happens to the stream right before this call
+    bool add_input = false; // x <- x + x0 right before this call (x0: the embedding's output), in the stream's dtype
 };
 
 // x <- W [x; x0] before a layer call: the stream and the embedding's output (after its norm and multiplier) side by
@@ -90,7 +91,8 @@ struct ModelSpec {
     // holds them once; every part is offered them by name after loading (Part::bind_shared).
     std::map<std::string, std::vector<int64_t>> shared;
     // true: the residual stream is kept in 32-bit floats whatever the activations' dtype; norms read it and write
-    // the activation dtype, products add into it in 32-bit.
+    // the activation dtype, products add into it in 32-bit.  Without an embedding norm the token rows times
+    // embed_scale go straight into 32-bit rows.
     bool residual_f32 = false;
     PartSpec final_norm;
     std::string head;                           // tensor name of the head [vocab, width]; empty: the token table
@@ -229,6 +231,9 @@ public:
     using Part::Part;
     // A rotary encoding: pairs (i, i + rotary_dim/2) of every q and k head turn by pos / denominators[i].
     virtual bool rotary(const float** denominators, int* rotary_dim) const { return false; }
+    // A rotary encoding of neighbouring pairs: (2i, 2i + 1) of the first `dims` dimensions turn by pos * frequencies[i]
+    // (a device table), cosine and sine multiplied by `multiplier`.  A mixer with a layout of its own hands these to its kernel.
+    virtual bool pairs(const float** frequencies, float* multiplier, int* dims) const { return false; }
     // Any other encoding changes q and k inside qkv [rows, (n_heads + 2 n_kv_heads) * head_dim] itself.
     virtual void apply(Ops& ops, Tensor& qkv, const StepContext& ctx, int n_heads, int n_kv_heads, int head_dim) {}
 };

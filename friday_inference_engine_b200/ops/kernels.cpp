@@ -103,7 +103,8 @@ FAMILY(AttentionWindow, attention_window, "attention_window", resolve(h, fam, "a
 FAMILY(Residual, residual, "residual", resolve(h, fam, "residual_norm_cast", t.norm_cast);
        resolve(h, fam, "residual_concat_cast", t.concat_cast); resolve(h, fam, "residual_add_scaled", t.add_scaled);
        resolve(h, fam, "residual_kv_store", t.kv_store); resolve(h, fam, "residual_token_input", t.token_input);
-       resolve(h, fam, "residual_gelu_table", t.gelu_table); resolve(h, fam, "residual_rms_add", t.rms_add);)
+       resolve(h, fam, "residual_gelu_table", t.gelu_table); resolve(h, fam, "residual_rms_add", t.rms_add);
+       resolve(h, fam, "residual_layernorm_cast", t.layernorm_cast); resolve(h, fam, "residual_embed_rows", t.embed_rows);)
 FAMILY(Recurrence, recurrence, "recurrence", resolve(h, fam, "recurrence_shift_mix", t.shift_mix);
        resolve(h, fam, "recurrence_tanh_rows", t.tanh_rows); resolve(h, fam, "recurrence_scan", t.scan);
        resolve(h, fam, "recurrence_scan_plan", t.scan_plan);
@@ -113,6 +114,11 @@ FAMILY(Routed, routed, "routed", resolve(h, fam, "routed_route", t.route);
        resolve(h, fam, "routed_down_combine", t.down_combine);
        resolve(h, fam, "routed_down_scratch_floats", t.down_scratch_floats);
        resolve(h, fam, "routed_sort_pairs", t.sort_pairs); resolve(h, fam, "routed_combine", t.combine);)
+FAMILY(Delta, delta, "delta", resolve(h, fam, "delta_conv_prepare", t.conv_prepare);
+       resolve(h, fam, "delta_conv_state", t.conv_state); resolve(h, fam, "delta_scan", t.scan);)
+FAMILY(AttentionLatent, attention_latent, "attention_latent", resolve(h, fam, "attention_latent_rotate_pairs", t.rotate_pairs);
+       resolve(h, fam, "attention_latent_prepare", t.prepare); resolve(h, fam, "attention_latent_head_linear", t.head_linear);
+       resolve(h, fam, "attention_latent", t.run);)
 FAMILY(AttentionMma, attention_mma, "attention_mma", resolve(h, fam, "attention_mma", t.run);
        resolve(h, fam, "attention_mma_clusters_at_once", t.clusters_at_once);)
 FAMILY(AttentionTc, attention_tc, "attention_tc", resolve(h, fam, "attention_tc", t.run);)

@@ -65,6 +65,8 @@ struct Residual {
                        int, int, float, float*, int, cudaStream_t);
     int (*gelu_table)(const float*, const int*, const void*, int, int, int, void*, int, int, int, cudaStream_t);
     int (*rms_add)(float*, const float*, const void*, int, int, int, float, cudaStream_t);
+    int (*layernorm_cast)(const void*, int, const void*, const void*, int, void*, int, int, int, float, cudaStream_t);
+    int (*embed_rows)(const int*, const void*, int, float*, int, int, int, float, cudaStream_t);
 };
 struct Recurrence {
     last_error_fn last_error;
@@ -76,7 +78,26 @@ struct Recurrence {
                 int, int, float, float, int, float*, int, cudaStream_t);
     int (*scan_plan)(int, int, int, int, int, long long*);
     int (*head_norm_gate)(const float*, const void*, int, void*, const void*, int, int, const int*, int, int, int, float, float, int,
-                          cudaStream_t);
+                          int, cudaStream_t);
+};
+struct Delta {
+    last_error_fn last_error;
+    int (*conv_prepare)(const void*, int, int, int, int, const void*, int, float*, const float*, long long, const int*, const int*,
+                        const int*, int, int, int, int, int, float, float, int, cudaStream_t);
+    int (*conv_state)(const void*, int, int, int, int, float*, long long, const int*, const int*, const int*, const int*, int, int, int,
+                      int, int, int, cudaStream_t);
+    int (*scan)(const float*, const void*, int, const void*, int, int, const void*, const void*, int, float*, float*, long long,
+                long long, const int*, const int*, const int*, const int*, int, int, int, int, int, int, cudaStream_t);
+};
+struct AttentionLatent {
+    last_error_fn last_error;
+    int (*rotate_pairs)(void*, int, const int*, const int*, const float*, float, int, int, int, int, int, int, cudaStream_t);
+    int (*prepare)(const void*, int, int, int, void*, float*, const void*, int, float, const int*, const int*, const float*, float, int,
+                   int, int, int, int, int, cudaStream_t);
+    int (*head_linear)(const void*, int, int, int, int, const void*, int, int, void*, int, int, int, const void*, int, int, const int*,
+                       int, int, int, int, cudaStream_t);
+    int (*run)(const float*, float*, const void*, const void*, const int*, int, int, const int*, const int*, const void*, int, int,
+               int, int, int, float, int, float*, int, cudaStream_t);
 };
 struct Routed {
     last_error_fn last_error;
@@ -118,6 +139,8 @@ const AttentionWindow& attention_window();
 const Residual& residual();
 const Recurrence& recurrence();
 const Routed& routed();
+const Delta& delta();
+const AttentionLatent& attention_latent();
 
 // Called with a family's name when its library is missing; returns 0 when it has built it.
 typedef int (*builder_fn)(const char* family);

@@ -232,6 +232,26 @@ Tensor Ops::linear_residual(const Rows& x, const Tensor& weight, const Tensor* b
     return add_scaled(residual, y, alpha);
 }
 
+Tensor Ops::layernorm_to(const Tensor& x, const Tensor& weight, const Tensor* bias, float eps, DType out_dtype) {
+    if (!x.contiguous() || weight.numel() != x.cols() || (bias && (bias->numel() != x.cols() || bias->dtype != weight.dtype)))
+        throw KernelError("layernorm: contiguous rows, a weight and a bias of their width and of one dtype");
+    Tensor o = alloc(out_dtype, x.rows(), x.cols());
+    const auto& k = kernels::residual();
+    Timed t(*this, Other);
+    call(launches_, k, k.layernorm_cast(x.data, code(x.dtype), weight.data, bias ? bias->data : nullptr, code(weight.dtype), o.data,
+                                        code(out_dtype), (int)x.rows(), (int)x.cols(), eps, stream_), "layernorm_cast");
+    return o;
+}
+
+Tensor Ops::embed_rows(const int* tokens, int64_t n, const Tensor& table, float scale) {
+    Tensor o = alloc(DType::F32, n, table.cols());
+    const auto& k = kernels::residual();
+    Timed t(*this, Other);
+    call(launches_, k, k.embed_rows(tokens, table.data, code(table.dtype), (float*)o.data, (int)n, (int)table.cols(), (int)table.rows(),
+                                    scale, stream_), "embed_rows");
+    return o;
+}
+
 void Ops::kv_store(const Tensor& src, int64_t k_off, int64_t v_off, const CacheView& view, const StepContext& ctx) {
     if (view.kind != CacheRequest::KV || !view.k_pool) throw KernelError("kv_store needs a view of keys and values");
     if (!view.write) return;
@@ -333,7 +353,7 @@ Tensor Ops::state_scan(const Tensor& q, const Tensor& kk, const Tensor& v, const
 }
 
 Tensor Ops::head_norm_gate(const Tensor& o, const Tensor& gate, const Tensor& weight, bool weight_per_head, int heads, int dv,
-                           float eps, float out_scale, DType dtype, const StepContext& ctx) {
+                           float eps, float out_scale, DType dtype, const StepContext& ctx, bool gate_sigmoid) {
     if (o.dtype != DType::F32 || !o.contiguous() || o.cols() != (int64_t)heads * dv || gate.dtype != dtype ||
         weight.numel() != (weight_per_head ? (int64_t)heads * dv : (int64_t)dv))
         throw KernelError("head_norm_gate: fp32 rows [rows, heads * dv], a gate in the result's dtype, a weight per channel");
@@ -341,8 +361,101 @@ Tensor Ops::head_norm_gate(const Tensor& o, const Tensor& gate, const Tensor& we
     const auto& k = kernels::recurrence();
     Timed t(*this, Other);
     call(launches_, k, k.head_norm_gate((const float*)o.data, gate.data, (int)gate.ld, out.data, weight.data, code(weight.dtype),
-                                        weight_per_head ? 1 : 0, ctx.row_seq, (int)o.rows(), heads, dv, eps, out_scale, code(dtype),
-                                        stream_), "head_norm_gate");
+                                        weight_per_head ? 1 : 0, ctx.row_seq, (int)o.rows(), heads, dv, eps, out_scale,
+                                        gate_sigmoid ? 1 : 0, code(dtype), stream_), "head_norm_gate");
+    return out;
+}
+
+// ------------------------------------------------------------------ the delta rule
+Tensor Ops::conv_silu_unit(const Tensor& proj, const Tensor& taps, const DeltaSpec& s, const CacheView& view, const StepContext& ctx) {
+    if (view.kind != CacheRequest::State || !view.state.defined() || view.state.dtype != DType::F32)
+        throw KernelError("conv_silu_unit needs a 32-bit state view");
+    const int64_t qk = (int64_t)s.qk_heads * s.dk, channels = 2 * qk + (int64_t)s.heads * s.dv;
+    const long long stride = view.state.numel() / view.state.shape[0];
+    if (taps.numel() != channels * s.taps || (int64_t)(s.taps - 1) * channels + (int64_t)s.heads * s.dk * s.dv > stride)
+        throw KernelError("conv_silu_unit: taps [channels, taps] and a state that holds taps - 1 rows of inputs before the heads' matrices");
+    Tensor out = alloc(DType::F32, proj.rows(), channels);
+    const auto& k = kernels::delta();
+    Timed t(*this, Other);
+    call(launches_, k, k.conv_prepare(proj.data, (int)proj.ld, (int)s.q_off, (int)s.k_off, (int)s.v_off, taps.data, code(taps.dtype),
+                                      (float*)out.data, (const float*)view.state.data, stride, ctx.row_seq, ctx.seq_start, view.seq_slots,
+                                      (int)proj.rows(), s.qk_heads, s.dk, s.heads * s.dv, s.taps, s.q_scale, s.unit_eps, code(proj.dtype),
+                                      stream_), "conv_prepare");
+    if (s.taps > 1)
+        call(launches_, k, k.conv_state(proj.data, (int)proj.ld, (int)s.q_off, (int)s.k_off, (int)s.v_off, (float*)view.state.data, stride,
+                                        ctx.row_seq, ctx.seq_start, ctx.seq_qlen, view.seq_slots, ctx.n_seqs, s.qk_heads, s.dk,
+                                        s.heads * s.dv, s.taps, code(proj.dtype), stream_), "conv_state");
+    return out;
+}
+
+Tensor Ops::delta_scan(const Tensor& qkv, const Tensor& a_raw, const Tensor& b_raw, const Tensor& a_log, const Tensor& dt_bias,
+                       const DeltaSpec& s, const CacheView& view, const StepContext& ctx) {
+    if (view.kind != CacheRequest::State || !view.state.defined() || view.state.dtype != DType::F32)
+        throw KernelError("delta_scan needs a 32-bit state view");
+    const int64_t channels = 2 * (int64_t)s.qk_heads * s.dk + (int64_t)s.heads * s.dv;
+    if (qkv.dtype != DType::F32 || !qkv.contiguous() || qkv.cols() != channels || a_raw.dtype != b_raw.dtype ||
+        a_log.numel() != s.heads || a_log.dtype != dt_bias.dtype || dt_bias.numel() != (s.per_channel ? (int64_t)s.heads * s.dk : (int64_t)s.heads))
+        throw KernelError("delta_scan: fp32 q, k, v rows, raw decays and betas of one dtype, a rate per head and a bias per decay");
+    const long long stride = view.state.numel() / view.state.shape[0];
+    const long long s_off = (long long)(s.taps - 1) * channels;
+    Tensor out = alloc(DType::F32, qkv.rows(), (int64_t)s.heads * s.dv);
+    const auto& k = kernels::delta();
+    Timed t(*this, Attention);
+    call(launches_, k, k.scan((const float*)qkv.data, a_raw.data, (int)a_raw.ld, b_raw.data, (int)b_raw.ld, code(a_raw.dtype), a_log.data,
+                              dt_bias.data, code(a_log.dtype), (float*)out.data, (float*)view.state.data, stride, s_off, ctx.row_seq,
+                              ctx.seq_start, ctx.seq_qlen, view.seq_slots, ctx.n_seqs, s.heads, s.qk_heads, s.dk, s.dv,
+                              s.per_channel ? 1 : 0, stream_), "delta_scan");
+    return out;
+}
+
+// ------------------------------------------------------------------ attention over a cached latent
+void Ops::rotate_pairs(Tensor& x, const StepContext& ctx, const float* freq, float mult, int heads, int64_t head_stride, int64_t first,
+                       int dims) {
+    const auto& k = kernels::attention_latent();
+    Timed t(*this, Other);
+    call(launches_, k, k.rotate_pairs(x.data, (int)x.ld, ctx.row_seq, ctx.row_pos, freq, mult, (int)x.rows(), heads, (int)head_stride,
+                                      (int)first, dims, code(x.dtype), stream_), "rotate_pairs");
+}
+
+Tensor Ops::latent_prepare(const Tensor& proj, const Tensor& norm_w, const LatentSpec& s, Tensor& qf, const StepContext& ctx) {
+    if (qf.dtype != DType::F32 || !qf.contiguous() || qf.cols() != (int64_t)s.heads * (s.rank + s.rot) || norm_w.numel() != s.rank)
+        throw KernelError("latent_prepare: fp32 queries [rows, heads * (rank + rot)] and a norm weight of the latent's size");
+    Tensor ckr = alloc(proj.dtype, proj.rows(), (int64_t)s.rank + s.rot);
+    const auto& k = kernels::attention_latent();
+    Timed t(*this, Other);
+    call(launches_, k, k.prepare(proj.data, (int)proj.ld, (int)s.q_off, (int)s.kv_off, ckr.data, (float*)qf.data, norm_w.data,
+                                 code(norm_w.dtype), s.eps, ctx.row_seq, ctx.row_pos, s.freq, s.rot_mult, (int)proj.rows(), s.heads, s.dim,
+                                 s.rot, s.rank, code(proj.dtype), stream_), "latent_prepare");
+    return ckr;
+}
+
+void Ops::head_linear(const Tensor& x, int64_t x_off, int64_t x_stride, const Tensor& w, bool per_head_rows_k, Tensor& out,
+                      int64_t out_stride, const Tensor* gate, int64_t gate_off, int heads, int k_, int n, const StepContext& ctx) {
+    if (!w.contiguous() || w.numel() != (int64_t)heads * k_ * n || (gate && gate->dtype != out.dtype))
+        throw KernelError("head_linear: contiguous weights of heads * k * n numbers, a gate in the result's dtype");
+    const auto& k = kernels::attention_latent();
+    Timed t(*this, Product);
+    call(launches_, k, k.head_linear(x.data, code(x.dtype), (int)x.ld, (int)x_off, (int)x_stride, w.data, code(w.dtype),
+                                     per_head_rows_k ? 0 : 1, out.data, code(out.dtype), (int)out.ld, (int)out_stride,
+                                     gate ? gate->data : nullptr, gate ? (int)gate->ld : 0, (int)gate_off, ctx.row_seq, (int)x.rows(),
+                                     heads, k_, n, stream_), "head_linear");
+}
+
+Tensor Ops::latent_attention(const Tensor& qf, const Tensor* sink, const LatentSpec& s, const CacheView& view, const StepContext& ctx) {
+    if (view.kind != CacheRequest::KV || !view.k_pool) throw KernelError("latent_attention needs a view of cached rows");
+    const int vd = view.v_head_dim > 0 ? view.v_head_dim : view.head_dim;
+    if (view.n_kv_heads != 1 || view.head_dim != s.rank || vd != s.rot || (sink && sink->numel() != s.heads))
+        throw KernelError("latent_attention: the cache keeps one row [latent | key part] per position, the sink one number per head");
+    const int rows = (int)qf.rows();
+    Tensor out = alloc(DType::F32, rows, (int64_t)s.heads * s.rank);
+    const int splits = attention_splits(rows, s.heads, ctx.max_kv_len);
+    float* scratch = splits > 1 ? scratch_floats((int64_t)rows * s.heads * splits * (s.rank + 2)) : nullptr;
+    const auto& k = kernels::attention_latent();
+    Timed t(*this, Attention);
+    call(launches_, k, k.run((const float*)qf.data, (float*)out.data, view.k_pool, view.v_pool, view.block_table, view.table_width,
+                             view.page_size, ctx.row_seq, ctx.row_pos, sink ? sink->data : nullptr, sink ? code(sink->dtype) : 0, rows,
+                             s.heads, s.rank, s.rot, s.scale, splits, scratch, code(view.dtype), stream_), "attention_latent");
+    if (splits > 1) ++launches_;
     return out;
 }
 

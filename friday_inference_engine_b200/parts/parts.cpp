@@ -1,11 +1,13 @@
 // The registry of parts, the description of a model as data, and the parts this library
-// ships: RMSNorm, rotary NeoX encoding (and "none"), grouped-query attention, the SwiGLU
+// ships: RMSNorm, layer norm, rotary encodings (NeoX halves, neighbouring pairs with stretched wavelengths, and "none"),
+// grouped-query attention, the SwiGLU
 // feed-forward and the pre-norm residual block.
 #include "friday/parts.h"
 
 #include <dlfcn.h>
 #include <math.h>
 
+#include <algorithm>
 #include <mutex>
 
 #include "friday/ops.h"
@@ -187,6 +189,34 @@ private:
     std::string name_;
 };
 
+// ------------------------------------------------------------------ layer norm
+// y = (x - mean) / sqrt(variance + eps) * weight + bias, mean and variance (the mean of the squared deviations) in fp32.
+// The weight's tensor is "weight_name" (default "weight"), the bias "bias_name" (default: the weight's name + ".b";
+// "bias": false leaves it out).  It reads whatever dtype the stream has and writes the activations'.
+class LayerNorm : public Norm {
+public:
+    LayerNorm(const PartSpec& s, const BuildEnv& e) : Norm(e) {
+        const Json* eps = s.params.find("eps");
+        if (!eps || !eps->is_number()) throw ConfigError("layernorm needs 'eps'");
+        eps_ = (float)eps->as_double();
+        width_ = s.params.get_int("width", e.width);
+        name_ = s.params.get_string("weight_name", "weight");
+        has_bias_ = s.params.get_bool("bias", true);
+        bias_name_ = s.params.get_string("bias_name", name_ + ".b");
+        declare(name_, {width_}, false, true);
+        if (has_bias_) declare(bias_name_, {width_});
+    }
+    Tensor forward(Ops& ops, const Tensor& x) override {
+        return ops.layernorm_to(x, tensor(name_), has_bias_ ? &tensor(bias_name_) : nullptr, eps_, env.dtype);
+    }
+
+private:
+    float eps_;
+    int64_t width_;
+    bool has_bias_;
+    std::string name_, bias_name_;
+};
+
 // ------------------------------------------------------------------ rotary encoding, NeoX pairing
 // The pair (i, i + rotary_dim/2) of every query and key head is rotated by the angle pos / theta^(2i / rotary_dim).
 // The angle is formed as the reference forms it (cuda_math_kernels.cu:337-339, cpu_ops.cpp:26-30): the denominator
@@ -232,6 +262,68 @@ private:
 class NoPosition : public Position {
 public:
     NoPosition(const PartSpec&, const BuildEnv& e) : Position(e) {}
+};
+
+// ------------------------------------------------------------------ rotary encoding, neighbouring pairs
+// The pair (2i, 2i + 1) of the first `dims` dimensions turns by pos * f_i, f_i = base^(-2i / dims).  With "scaling"
+// {factor, original, fast, slow} long wavelengths are stretched: with dim(t) = dims ln(original / (2 pi t)) / (2 ln base),
+// lo = max(floor(dim(fast)), 0), hi = min(ceil(dim(slow)), dims - 1) and ramp_i = clamp((i - lo) / max(hi - lo, 0.001), 0, 1)
+// the frequency is f_i / factor * ramp_i + f_i (1 - ramp_i), and cosine and sine are multiplied by 0.1 ln(factor) + 1.
+// The table is made once on the host in double precision and rounded to fp32; the angle is fp32(pos) * f_i in the kernel.
+class RotaryPairs : public Position {
+public:
+    RotaryPairs(const PartSpec& s, const BuildEnv& e) : Position(e) {
+        const double base = s.params.get_double("base", 0);
+        dims_ = (int)s.params.get_int("dims", 0);
+        if (base <= 1.0) throw ConfigError("rotary_pairs: 'base' must be greater than 1");
+        if (dims_ <= 0 || dims_ % 2) throw ConfigError(format("rotary_pairs: 'dims' = %d must be even and positive", dims_));
+        const int half = dims_ / 2;
+        table_.resize(half);
+        std::vector<double> f(half);
+        for (int i = 0; i < half; ++i) f[i] = pow(base, -2.0 * i / dims_);
+        const Json* sc = s.params.find("scaling");
+        if (sc && sc->is_object()) {
+            const double factor = sc->get_double("factor", 1.0), original = sc->get_double("original", 0);
+            const double fast = sc->get_double("fast", 32.0), slow = sc->get_double("slow", 1.0);
+            if (!(factor > 0) || !(original > 0) || !(fast > 0) || !(slow > 0))
+                throw ConfigError("rotary_pairs: 'scaling' needs positive factor, original, fast and slow");
+            auto dim_of = [&](double turns) { return dims_ * log(original / (2.0 * M_PI * turns)) / (2.0 * log(base)); };
+            const double lo = std::max(floor(dim_of(fast)), 0.0), hi = std::min(ceil(dim_of(slow)), (double)dims_ - 1.0);
+            for (int i = 0; i < half; ++i) {
+                double ramp = ((double)i - lo) / std::max(hi - lo, 0.001);
+                ramp = ramp < 0 ? 0 : (ramp > 1 ? 1 : ramp);
+                f[i] = f[i] / factor * ramp + f[i] * (1.0 - ramp);
+            }
+            mult_ = (float)(0.1 * log(factor) + 1.0);
+        }
+        for (int i = 0; i < half; ++i) table_[i] = (float)f[i];
+    }
+    void finalize(Ops& ops) override {
+        Position::finalize(ops);
+        auto mem = std::make_shared<DeviceBuffer>(table_.size() * sizeof(float));
+        cuda_check(cudaMemcpyAsync(mem->get(), table_.data(), table_.size() * sizeof(float), cudaMemcpyHostToDevice, ops.stream()),
+                   "cudaMemcpyAsync");
+        cuda_check(cudaStreamSynchronize(ops.stream()), "cudaStreamSynchronize");
+        freq_ = (const float*)mem->get();
+        hold(mem);
+    }
+    bool pairs(const float** frequencies, float* multiplier, int* dims) const override {
+        *frequencies = freq_;
+        *multiplier = mult_;
+        *dims = dims_;
+        return true;
+    }
+    // inside a stacked q/k/v buffer: every query and key head's first `dims` dimensions
+    void apply(Ops& ops, Tensor& qkv, const StepContext& ctx, int n_heads, int n_kv_heads, int head_dim) override {
+        if (dims_ > head_dim) throw ConfigError(format("rotary_pairs: %d rotated dimensions in heads of %d", dims_, head_dim));
+        ops.rotate_pairs(qkv, ctx, freq_, mult_, n_heads + n_kv_heads, head_dim, 0, dims_);
+    }
+
+private:
+    int dims_;
+    float mult_ = 1.0f;
+    std::vector<float> table_;
+    const float* freq_ = nullptr;
 };
 
 // ------------------------------------------------------------------ grouped-query attention over the paged cache
@@ -344,24 +436,32 @@ public:
     SwiGLU(const PartSpec& s, const BuildEnv& e) : FeedForward(e) {
         inner_ = s.params.get_int("inner", 0);
         if (inner_ <= 0) throw ConfigError("swiglu needs 'inner'");
+        // tensor names: Hugging Face's unless the specification gives others ("names": {"gate": ..., "up": ..., "down": ...})
+        const Json* names = s.params.find("names");
+        auto name_of = [&](const char* role, const char* fallback) {
+            return names && names->is_object() && names->has(role) ? names->at(role).as_string() : std::string(fallback);
+        };
+        down_ = name_of("down", "down_proj.weight");
         declare_stacked("w_gate_up", 2 * inner_, e.width);
-        declare("gate_proj.weight", {inner_, e.width}).stack("w_gate_up", 0, 2);
-        declare("up_proj.weight", {inner_, e.width}).stack("w_gate_up", 1, 2);
-        declare("down_proj.weight", {e.width, inner_});
+        declare(name_of("gate", "gate_proj.weight"), {inner_, e.width}).stack("w_gate_up", 0, 2);
+        declare(name_of("up", "up_proj.weight"), {inner_, e.width}).stack("w_gate_up", 1, 2);
+        declare(down_, {e.width, inner_});
     }
     PartOut forward(Ops& ops, const Rows& h, const Tensor& residual, const StepContext&, Norm* then) override {
         Tensor inner = ops.linear_swiglu(h, tensor("w_gate_up"));
         Tensor nw;
         float eps;
-        if (then && then->as_rmsnorm(&nw, &eps)) {
-            auto r = ops.linear_norm(Rows(inner), tensor("down_proj.weight"), nw, eps, nullptr, &residual);
+        if (then && residual.dtype == inner.dtype && then->as_rmsnorm(&nw, &eps)) {
+            auto r = ops.linear_norm(Rows(inner), tensor(down_), nw, eps, nullptr, &residual);
             return PartOut(r.first, r.second);
         }
-        return PartOut(ops.linear(Rows(inner), tensor("down_proj.weight"), nullptr, &residual));
+        // a 32-bit stream beside 16-bit activations: the product's result stays 32-bit and is added there
+        return PartOut(ops.linear_residual(Rows(inner), tensor(down_), nullptr, residual));
     }
 
 private:
     int64_t inner_;
+    std::string down_;
 };
 
 // ------------------------------------------------------------------ pre-norm residual block
@@ -420,6 +520,8 @@ private:
 
 namespace {
 PartRegistrar r1("norm", "rmsnorm", [](const PartSpec& s, const BuildEnv& e) -> Part* { return new RMSNorm(s, e); });
+PartRegistrar r1b("norm", "layernorm", [](const PartSpec& s, const BuildEnv& e) -> Part* { return new LayerNorm(s, e); });
+PartRegistrar r2b("position", "rotary_pairs", [](const PartSpec& s, const BuildEnv& e) -> Part* { return new RotaryPairs(s, e); });
 PartRegistrar r2("position", "rotary_neox", [](const PartSpec& s, const BuildEnv& e) -> Part* { return new RotaryNeox(s, e); });
 PartRegistrar r3("position", "none", [](const PartSpec& s, const BuildEnv& e) -> Part* { return new NoPosition(s, e); });
 PartRegistrar r4("mixer", "gqa_attention", [](const PartSpec& s, const BuildEnv& e) -> Part* { return new GQAttention(s, e); });

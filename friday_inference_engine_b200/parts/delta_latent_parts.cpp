@@ -68,25 +68,26 @@ public:
         declare("k", {qk, w}).stack("w_in", qk);
         declare("v", {hv, w}).stack("w_in", 2 * qk);
         if (!low_rank_gate_) declare("g", {hv, w}).stack("w_in", 2 * qk + hv);
-        if (taps_ > 1) {
-            declare_stacked("taps", 2 * qk + hv, taps_);
-            declare("q.conv", {qk, (int64_t)taps_}).stack("taps", 0);
-            declare("k.conv", {qk, (int64_t)taps_}).stack("taps", qk);
-            declare("v.conv", {hv, (int64_t)taps_}).stack("taps", 2 * qk);
-        }
+        // a convolution of one tap is a multiplier per channel and keeps no history
+        declare_stacked("taps", 2 * qk + hv, taps_);
+        declare("q.conv", {qk, (int64_t)taps_}).stack("taps", 0);
+        declare("k.conv", {qk, (int64_t)taps_}).stack("taps", qk);
+        declare("v.conv", {hv, (int64_t)taps_}).stack("taps", 2 * qk);
         // what enters the recurrence: beta (and the per-head decay) in one product whose result stays 32-bit
         small_rows_ = heads_ + (per_channel_ ? 0 : heads_);
         declare_stacked("w_rec", small_rows_, w);
         declare("b", {(int64_t)heads_, w}).stack("w_rec", 0);
         if (!per_channel_) declare("a", {(int64_t)heads_, w}).stack("w_rec", heads_);
-        // the inner sizes of the two-step projections are the checkpoint's to give
+        // the inner sizes of the two-step projections are the checkpoint's to give unless "decay_rank" / "gate_rank" name them
+        const int64_t decay_rank = s.params.get_int("decay_rank", -1) > 0 ? s.params.get_int("decay_rank", -1) : -1;
+        const int64_t gate_rank = s.params.get_int("gate_rank", -1) > 0 ? s.params.get_int("gate_rank", -1) : -1;
         if (per_channel_) {
-            declare("a1", {-1, w});
-            declare("a2", {(int64_t)heads_ * dk_, -1});
+            declare("a1", {decay_rank, w});
+            declare("a2", {(int64_t)heads_ * dk_, decay_rank});
         }
         if (low_rank_gate_) {
-            declare("g1", {-1, w});
-            declare("g2", {hv, -1});
+            declare("g1", {gate_rank, w});
+            declare("g2", {hv, gate_rank});
         }
         declare("A_log", {(int64_t)heads_});
         declare("dt_bias", {per_channel_ ? (int64_t)heads_ * dk_ : (int64_t)heads_});
@@ -101,15 +102,6 @@ public:
         Mixer::finalize(ops);
         if (per_channel_ && tensor("a1").rows() != tensor("a2").cols()) throw ConfigError(prefix + ": the decay's two projections do not fit each other");
         if (low_rank_gate_ && tensor("g1").rows() != tensor("g2").cols()) throw ConfigError(prefix + ": the gate's two projections do not fit each other");
-        if (taps_ == 1) {                          // no convolution: a single tap of one
-            const int64_t channels = 2 * (int64_t)qk_heads_ * dk_ + (int64_t)heads_ * dv_;
-            std::vector<float> ones((size_t)channels, 1.0f);
-            auto mem = std::make_shared<DeviceBuffer>(ones.size() * sizeof(float));
-            cuda_check(cudaMemcpyAsync(mem->get(), ones.data(), ones.size() * sizeof(float), cudaMemcpyHostToDevice, ops.stream()), "cudaMemcpyAsync");
-            cuda_check(cudaStreamSynchronize(ops.stream()), "cudaStreamSynchronize");
-            set_tensor("taps", Tensor::make(mem->get(), DType::F32, {channels, 1}));
-            hold(mem);
-        }
     }
 
     PartOut forward(Ops& ops, const Rows& h, const Tensor& residual, const StepContext& ctx, const CacheView& view, Norm*) override {

@@ -253,3 +253,11 @@ def forward(cfg, W, tokens, streams=None):
             streams.append(X.copy())
     h = layer_norm(X, W["final.norm"], W["final.norm.b"], float(cfg["norm"]["eps"]))
     return h @ W["embed"].T
+
+
+def greedy(cfg, W, prompt, n_new):
+    """The tokens that greedy decoding appends to `prompt` (the first maximum wins)."""
+    tokens = list(prompt)
+    for _ in range(n_new):
+        tokens.append(int(np.argmax(forward(cfg, W, tokens)[-1])))
+    return tokens[len(prompt):]

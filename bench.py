@@ -557,6 +557,53 @@ def tikunex_config(width, layers=4, vocab=32768, window=1024, experts=8, top=2):
             "loop": {"start": 1, "stop": layers, "times": 2}, "token_side": {"dim": 64}}
 
 
+def beletar_config(width, layers=4, vocab=32768):
+    """A Beletar configuration whose layers have sizes like a real model's of this width: attention over a latent of 512
+    with a rotated part of 64, heads of 128; delta-rule layers with heads of 128 x 128 on half as many query/key heads,
+    convolutions of four taps; a gated feed-forward of three times the width everywhere; the last three layers run twice."""
+    heads = max(1, width // 128)
+    lat = {"heads": heads, "dim": 128, "rot_dim": 64, "vdim": 128, "kv_rank": 512, "scale": 192 ** -0.5,
+           "rot": {"base": 10000.0, "dims": 64, "scaling": {"factor": 4.0, "original": 4096, "fast": 32.0, "slow": 1.0}}}
+    dl = {"heads": heads, "kv_heads": max(1, heads // 2), "dim": 128, "vdim": 128, "conv": 4}
+    ch = dict(dl, decay_rank=64, gate_rank=64)
+    mlp = {"kind": "dense", "ff": 3 * width}
+    kinds = [("latent_attention", lat), ("delta", dl), ("delta", dl), ("channel_delta", ch)]
+    ls = [{"type": kinds[i % 4][0], "mixer": kinds[i % 4][1], "mlp": mlp} for i in range(layers)]
+    return {"architecture": "Beletar", "vocab": vocab, "width": width, "norm": {"eps": 1e-5}, "embedding": {"scale": 1.0},
+            "layers": ls, "loop": {"start": 1, "stop": layers, "times": 2}}
+
+
+def beletar_numbers(cfg, batch, context, prompt_len):
+    """What a decode step of `batch` sequences must read and what a prompt token costs (the attention's share for a prompt
+    of prompt_len tokens, counted for keys and values expanded per head, the cheaper form for prompts)."""
+    w, v = cfg["width"], cfg["vocab"]
+    loop = cfg.get("loop") or {"start": 0, "stop": 0, "times": 1}
+    runs = [1 + (loop["times"] - 1) * (loop["start"] <= i < loop["stop"]) for i in range(len(cfg["layers"]))]
+    weight_bytes = 2 * v * w
+    state_bytes = kv_bytes = 0
+    flops = 2 * v * w
+    for L, n in zip(cfg["layers"], runs):
+        m = L["mixer"]
+        if L["type"] == "latent_attention":
+            H, d, r, vd, rank = m["heads"], m["dim"], m["rot_dim"], m["vdim"], m["kv_rank"]
+            mat = (H * (d + r) + rank + r + H) * w + H * (d + vd) * rank + w * H * vd
+            kv_bytes += n * batch * context * (rank + r) * 2
+            mix = 2 * H * (d + r + vd) * prompt_len // 2
+        else:
+            H, G, dk, dv = m["heads"], m["kv_heads"], m["dim"], m["vdim"]
+            mat = (2 * G * dk + H * dv) * w + H * w + w * H * dv
+            if L["type"] == "channel_delta":
+                mat += m["decay_rank"] * (w + H * dk) + m["gate_rank"] * (w + H * dv)
+            else:
+                mat += H * w + H * dv * w
+            state_bytes += n * batch * (H * dk * dv + (m["conv"] - 1) * (2 * G * dk + H * dv)) * 4 * 2
+            mix = 7 * H * dk * dv
+        ff = 3 * L["mlp"]["ff"] * w if L.get("mlp") else 0
+        weight_bytes += n * 2 * (mat + ff)             # a layer's weights are read again in every pass of the loop
+        flops += n * (2 * (mat + ff) + mix)
+    return {"step_bytes": weight_bytes + state_bytes + kv_bytes, "flops_per_token": flops}
+
+
 def tikunex_numbers(cfg, batch, context):
     """What a decode step of `batch` sequences must read and what a prompt token costs, per run of the layers."""
     w, v = cfg["width"], cfg["vocab"]
@@ -602,20 +649,27 @@ def tikunex_numbers(cfg, batch, context):
 
 
 def design_compare(Engine, args):
-    """Tikunex beside the Qwen2.5 dense decoder at equal width and depth (random weights): one prompt and decode steps,
-    with the share of each kind of kernel in the prompt (event-bracketed).  One line of text per measurement."""
+    """Beletar and Tikunex beside the Qwen2.5 dense decoder at equal width and depth (random weights): one prompt and decode
+    steps, with the share of each kind of kernel in the prompt (event-bracketed).  One line of text per measurement.
+    --designs picks among them."""
     pk = peaks()
     prompt_len, batch, context = 2048, args.batch, 1024
     for width in [int(v) for v in args.design_compare.split(",") if v]:
         layers = args.layers or 4
         designs = [
+            ("beletar", beletar_config(width, layers)),
             ("tikunex", tikunex_config(width, layers)),
             ("qwen2", dict(QWEN25_7B, num_hidden_layers=2 * layers - 1, hidden_size=width, num_attention_heads=width // 128,
                            num_key_value_heads=max(1, width // 512), intermediate_size=3 * width, vocab_size=32768)),
         ]
         for name, cfg in designs:
+            if name not in args.designs.split(","):
+                continue
             eng = Engine(config=cfg, seed=0, dtype="bfloat16", max_ctx=4096, max_batch=batch, max_tokens=batch * 4096 + 8192)
-            if name == "tikunex":
+            if name == "beletar":
+                nums = beletar_numbers(cfg, batch, context + 64, prompt_len)
+                flops_tok, step_bytes = nums["flops_per_token"], nums["step_bytes"]
+            elif name == "tikunex":
                 nums = tikunex_numbers(cfg, batch, context + 64)
                 flops_tok, step_bytes = nums["flops_per_token"], nums["step_bytes"]
             else:
@@ -679,8 +733,9 @@ def main():
     ap.add_argument("--prefill-chunk", type=int, default=0, dest="prefill_chunk",
                     help="most tokens of a sequence per pass in the sweeps (0: the engine's own)")
     ap.add_argument("--design-compare", default="", dest="design_compare",
-                    help="widths, e.g. 1024,2048,4096: a Tikunex model with layers of that size beside the Qwen2.5 decoder of "
-                         "equal width (prompt, decode steps, kernel shares): lines of text")
+                    help="widths, e.g. 1024,2048,4096: a Beletar and a Tikunex model with layers of that size beside the Qwen2.5 "
+                         "decoder of equal width (prompt, decode steps, kernel shares): lines of text")
+    ap.add_argument("--designs", default="beletar,tikunex,qwen2", help="which designs --design-compare runs")
     ap.add_argument("--timeline", action="store_true",
                     help="print the kernels of one decode step as they run inside the captured graph (torch profiler)")
     args = ap.parse_args()

@@ -122,6 +122,11 @@ PartSpec delta_spec(const Json& m, double eps, bool per_channel) {
     p.set("eps", Json(eps));
     p.set("decay", Json(per_channel ? "channel" : "head"));
     p.set("gate", Json(per_channel ? "low_rank" : "full"));
+    // optional: the inner sizes of the two-step projections, for drawing random weights (a checkpoint's shapes give them)
+    for (const char* k : {"decay_rank", "gate_rank"}) {
+        const Json* r = m.find(k);
+        if (r && r->is_int() && r->as_int() > 0) p.set(k, *r);
+    }
     return PartSpec("gated_delta", p, "mix.");
 }
 

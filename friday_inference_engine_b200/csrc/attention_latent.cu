@@ -394,6 +394,92 @@ __global__ void __launch_bounds__(128) latent_merge_kernel(AttnArgs p) {
     }
 }
 
+// ------------------------------------------------------------------ prompts: the pieces between tensor-core products
+// Rows [0, n) of one sequence's cached latents and key parts, gathered from the pages into contiguous rows; rows
+// [n, n_pad) are zero.
+template <typename T>
+__global__ void gather_kernel(const T* __restrict__ c_pool, const T* __restrict__ r_pool, const int* __restrict__ table, int page,
+                              int n, int rank, int rot, T* __restrict__ c_all, T* __restrict__ r_all) {
+    fr_pdl_wait();
+    fr_pdl_launch();
+    const int j = blockIdx.x;
+    T* c = c_all + (size_t)j * rank;
+    T* r = r_all + (size_t)j * rot;
+    if (j >= n) {
+        for (int i = threadIdx.x; i < rank; i += blockDim.x) fr_store(c + i, 0.f);
+        for (int i = threadIdx.x; i < rot; i += blockDim.x) fr_store(r + i, 0.f);
+        return;
+    }
+    const size_t at = (size_t)table[j / page] * page + j % page;
+    for (int i = threadIdx.x; i < rank; i += blockDim.x) c[i] = c_pool[at * rank + i];
+    for (int i = threadIdx.x; i < rot; i += blockDim.x) r[i] = r_pool[at * rot + i];
+}
+
+// Row r of scores [rows][ld] (fp32, unscaled) belongs to position pos0 + r and sees keys 0 .. pos0 + r.  Its softmax
+// (scores times scale, the sink in the denominator) is written as two bf16 numbers per weight, p = hi + lo, so that the
+// product with the values keeps the weights' 32-bit precision in effect; keys out of sight get zeros.
+__global__ void __launch_bounds__(256) softmax_split_kernel(const float* __restrict__ s, int ld, int n_pad, int pos0, float scale,
+                                                            const void* sink, int sink_dtype, int head, bf16* __restrict__ hi,
+                                                            bf16* __restrict__ lo) {
+    __shared__ float red[8];
+    __shared__ float bc;
+    fr_pdl_wait();
+    fr_pdl_launch();
+    const int row = blockIdx.x;
+    const int n = min(pos0 + row + 1, n_pad);
+    const float* sr = s + (size_t)row * ld;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    float m = -INFINITY;
+    for (int j = threadIdx.x; j < n; j += blockDim.x) m = fmaxf(m, sr[j] * scale);
+    m = fr_warp_max(m);
+    if (lane == 0) red[warp] = m;
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        float t = red[0];
+        for (int i = 1; i < 8; ++i) t = fmaxf(t, red[i]);
+        if (sink != nullptr) t = fmaxf(t, FrVec{sink, sink_dtype}.at(head));
+        bc = t;
+    }
+    __syncthreads();
+    m = bc;
+    float l = 0.f;
+    for (int j = threadIdx.x; j < n; j += blockDim.x) l += expf(sr[j] * scale - m);
+    l = fr_warp_sum(l);
+    __syncthreads();
+    if (lane == 0) red[warp] = l;
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        float t = 0.f;
+        for (int i = 0; i < 8; ++i) t += red[i];
+        if (sink != nullptr) t += expf(FrVec{sink, sink_dtype}.at(head) - m);
+        bc = 1.0f / t;
+    }
+    __syncthreads();
+    const float inv = bc;
+    bf16* h = hi + (size_t)row * n_pad;
+    bf16* o = lo + (size_t)row * n_pad;
+    for (int j = threadIdx.x; j < n_pad; j += blockDim.x) {
+        const float p = j < n ? expf(sr[j] * scale - m) * inv : 0.f;
+        const bf16 ph = __float2bfloat16_rn(p);
+        h[j] = ph;
+        o[j] = __float2bfloat16_rn(p - __bfloat162float(ph));
+    }
+}
+
+// out[row][h * vd + n] = x[row][h * vd + n] * sigmoid(gate[row][gate_off + h]) (gate null: 1), fp32 -> T
+template <typename T>
+__global__ void gate_cast_kernel(const float* __restrict__ x, const T* __restrict__ gate, int ld_gate, int gate_off, int heads, int vd,
+                                 T* __restrict__ out) {
+    fr_pdl_wait();
+    fr_pdl_launch();
+    const size_t row = blockIdx.x;
+    for (int i = threadIdx.x; i < heads * vd; i += blockDim.x) {
+        float v = x[row * heads * vd + i];
+        if (gate != nullptr) v *= 1.0f / (1.0f + expf(-fr_load(gate + row * ld_gate + gate_off + i / vd)));
+        fr_store(out + row * heads * vd + i, v);
+    }
+}
+
 }  // namespace
 
 FR_EXPORT int attention_latent_rotate_pairs(void* x, int ld, const int* row_seq, const int* row_pos, const float* freq, float mult,
@@ -462,5 +548,36 @@ FR_EXPORT int attention_latent(const float* q, float* out, const void* c_pool, c
         FR_CUDA(fr_launch(latent_merge_kernel, dim3((items + 3) / 4), dim3(128), 0, stream, p));
         FR_CHECK_LAUNCH("latent attention merge");
     }
+    return FR_OK;
+}
+
+// One sequence's cached rows 0 .. n-1 (table: the sequence's row of the block table) as contiguous [n_pad][rank] and
+// [n_pad][rot]; rows from n on are zero.
+FR_EXPORT int attention_latent_gather(const void* c_pool, const void* r_pool, const int* table, int page, int n, int n_pad, int rank,
+                                      int rot, void* c_all, void* r_all, int dtype, cudaStream_t stream) {
+    if (n_pad <= 0) return FR_OK;
+    if (dtype == FR_F32) FR_CUDA(fr_launch(gather_kernel<float>, dim3(n_pad), dim3(128), 0, stream, (const float*)c_pool, (const float*)r_pool, table, page, n, rank, rot, (float*)c_all, (float*)r_all));
+    else if (dtype == FR_BF16) FR_CUDA(fr_launch(gather_kernel<bf16>, dim3(n_pad), dim3(128), 0, stream, (const bf16*)c_pool, (const bf16*)r_pool, table, page, n, rank, rot, (bf16*)c_all, (bf16*)r_all));
+    else FR_REFUSE("latent gather: unknown dtype %d", dtype);
+    FR_CHECK_LAUNCH("latent gather");
+    return FR_OK;
+}
+
+FR_EXPORT int attention_latent_softmax_split(const float* scores, int ld, int rows, int n_pad, int pos0, float scale, const void* sink,
+                                             int sink_dtype, int head, void* hi, void* lo, cudaStream_t stream) {
+    if (rows <= 0) return FR_OK;
+    FR_CUDA(fr_launch(softmax_split_kernel, dim3(rows), dim3(256), 0, stream, scores, ld, n_pad, pos0, scale, sink, sink_dtype, head,
+                      (bf16*)hi, (bf16*)lo));
+    FR_CHECK_LAUNCH("softmax_split");
+    return FR_OK;
+}
+
+FR_EXPORT int attention_latent_gate_cast(const float* x, const void* gate, int ld_gate, int gate_off, int rows, int heads, int vd,
+                                         void* out, int dtype, cudaStream_t stream) {
+    if (rows <= 0) return FR_OK;
+    if (dtype == FR_F32) FR_CUDA(fr_launch(gate_cast_kernel<float>, dim3(rows), dim3(256), 0, stream, x, (const float*)gate, ld_gate, gate_off, heads, vd, (float*)out));
+    else if (dtype == FR_BF16) FR_CUDA(fr_launch(gate_cast_kernel<bf16>, dim3(rows), dim3(256), 0, stream, x, (const bf16*)gate, ld_gate, gate_off, heads, vd, (bf16*)out));
+    else FR_REFUSE("gate_cast: unknown dtype %d", dtype);
+    FR_CHECK_LAUNCH("gate_cast");
     return FR_OK;
 }

@@ -13,8 +13,9 @@
 //                  the sequence's state, zeros at a sequence's start), then silu; every q and k head is made a unit
 //                  vector x / sqrt(sum x^2 + unit_eps), q is multiplied by q_scale.  Results are fp32.
 //   conv_state     the last taps-1 inputs of every sequence become its state's history (after conv_prepare has read it)
-//   scan           the recurrence, per (sequence, head): a thread owns one value channel (a column of S, dk numbers in
-//                  registers), tokens are staged through shared memory eight at a time.  beta = sigmoid(raw),
+//   scan           the recurrence, per (sequence, head): four threads share one value channel (a column of S, a quarter of its
+//                  dk numbers in each thread's registers); other warps of the block stage the next eight tokens through shared
+//                  memory meanwhile.  beta = sigmoid(raw),
 //                  g = exp(-exp(A_log) * softplus(raw + dt_bias)) are formed here in fp32.  Columns of S never mix, so
 //                  any split of the value channels over blocks is exact.
 //
@@ -162,17 +163,28 @@ __device__ __forceinline__ float softplus_f(float z) { return fmaxf(z, 0.f) + lo
 template <typename TR>
 __device__ __forceinline__ float raw_at(const void* p, size_t i) { return fr_load((const TR*)p + i); }
 
+constexpr int STAGE_THREADS = 128;   // warps that only stage tokens, beside the warps that own value channels
+constexpr int PARTS = 4;             // threads that share a value channel: each owns a quarter of the key channels
+
+// The first PARTS * p.cols threads walk the tokens: lanes (part, channel) of a warp own 8 value channels, four lanes each,
+// with the key channels dealt out in groups of four (part p owns groups p, p + 4, ...: neighbouring lanes read neighbouring
+// 16-byte pieces of shared memory); what the state holds along the key, and the read-out, are summed over the four lanes
+// with two shuffles.  The other STAGE_THREADS threads stage the next SCAN_TOKENS tokens (q, k, decays, betas, values) into
+// the other half of shared memory meanwhile, so that the chain never waits for global memory.  One barrier per SCAN_TOKENS
+// tokens.
 template <typename TR, int DK, bool PER_CHANNEL>
 __global__ void delta_scan_kernel(ScanArgs p) {
     extern __shared__ float sm[];
-    float* sq = sm;                                   // [SCAN_TOKENS][DK]
-    float* sk = sq + SCAN_TOKENS * DK;
-    float* sg = sk + SCAN_TOKENS * DK;                // [SCAN_TOKENS][DK] decays (per channel), or [SCAN_TOKENS] (per head)
-    float* sb = sg + (PER_CHANNEL ? SCAN_TOKENS * DK : SCAN_TOKENS);       // [SCAN_TOKENS] beta
-    float* sv = sb + SCAN_TOKENS;                     // [SCAN_TOKENS][threads]
+    constexpr int G_FLOATS = PER_CHANNEL ? SCAN_TOKENS * DK : SCAN_TOKENS;
+    constexpr int PER = DK / PARTS;                   // key channels per thread
+    const int buf_floats = 2 * SCAN_TOKENS * DK + G_FLOATS + SCAN_TOKENS + SCAN_TOKENS * p.cols;
     const int seq = blockIdx.x, head = blockIdx.y;
-    const int col = blockIdx.z * p.cols + threadIdx.x;
-    const bool live_col = threadIdx.x < p.cols && col < p.dv;
+    const int walkers = PARTS * p.cols;
+    const bool consumer = (int)threadIdx.x < walkers;
+    const int lane = threadIdx.x & 31, part = lane >> 3;
+    const int local_col = (threadIdx.x >> 5) * 8 + (lane & 7);
+    const int col = blockIdx.z * p.cols + local_col;
+    const bool live_col = consumer && col < p.dv;
     const int r0 = p.seq_start[seq], n = p.seq_qlen[seq];
     fr_pdl_wait();
     fr_pdl_launch();
@@ -180,106 +192,163 @@ __global__ void delta_scan_kernel(ScanArgs p) {
     const int group = head / (p.heads / p.qk_heads);
     const int qk = p.qk_heads * p.dk, channels = 2 * qk + p.heads * p.dv;
     float* S = p.state + (size_t)p.seq_slots[seq] * p.state_stride + p.s_off + (size_t)head * p.dk * p.dv;
-    float s[DK];
+    float s[PER];                                     // s[4 m + e]: key channel 4 (PARTS m + part) + e
 #pragma unroll
-    for (int i = 0; i < DK; ++i) s[i] = (live_col && i < p.dk) ? S[(size_t)i * p.dv + col] : 0.f;
+    for (int j = 0; j < PER; ++j) {
+        const int i = 4 * (PARTS * (j >> 2) + part) + (j & 3);
+        s[j] = (live_col && i < p.dk) ? S[(size_t)i * p.dv + col] : 0.f;
+    }
     const FrVec alog{p.a_log, p.vec_dtype}, dtb{p.dt_bias, p.vec_dtype};
     const float rate = expf(alog.at(head));
-    for (int t0 = 0; t0 < n; t0 += SCAN_TOKENS) {
+    const int chunks = (n + SCAN_TOKENS - 1) / SCAN_TOKENS;
+    const int n_cols = min(p.cols, p.dv - (int)blockIdx.z * p.cols);
+
+    // stages tokens [t0, t0 + nt) into buffer b: thread `who` of the STAGE_THREADS staging threads.  All of a thread's
+    // loads are issued before any of them is used, so that a chunk costs one trip to memory, not one per element.
+    auto stage = [&](int t0, int b, int who) {
+        float* sq = sm + (size_t)b * buf_floats;
+        float* sk = sq + SCAN_TOKENS * DK;
+        float* sg = sk + SCAN_TOKENS * DK;
+        float* sb = sg + G_FLOATS;
+        float* sv = sb + SCAN_TOKENS;
         const int nt = min(SCAN_TOKENS, n - t0);
-        __syncthreads();
-        for (int idx = threadIdx.x; idx < nt * DK; idx += blockDim.x) {
+        constexpr int N_IT = (SCAN_TOKENS * DK + STAGE_THREADS - 1) / STAGE_THREADS;
+        float qv[N_IT], kv[N_IT], gz[N_IT];
+#pragma unroll
+        for (int it = 0; it < N_IT; ++it) {
+            const int idx = who + it * STAGE_THREADS;
             const int t = idx / DK, i = idx - t * DK;
             const size_t row = (size_t)(r0 + t0 + t);
-            float qv = 0.f, kv = 0.f, gv = 1.f;
-            if (i < p.dk) {
-                qv = p.qkv[row * channels + group * p.dk + i];
-                kv = p.qkv[row * channels + qk + group * p.dk + i];
-                if (PER_CHANNEL) {
-                    const float z = raw_at<TR>(p.a_raw, row * p.ld_a + head * p.dk + i) + dtb.at(head * p.dk + i);
-                    gv = expf(-rate * softplus_f(z));
-                }
+            qv[it] = 0.f; kv[it] = 0.f; gz[it] = 0.f;
+            if (t < nt && i < p.dk) {
+                qv[it] = p.qkv[row * channels + group * p.dk + i];
+                kv[it] = p.qkv[row * channels + qk + group * p.dk + i];
+                if (PER_CHANNEL) gz[it] = raw_at<TR>(p.a_raw, row * p.ld_a + head * p.dk + i);
             }
-            sq[idx] = qv;
-            sk[idx] = kv;
-            if (PER_CHANNEL) sg[idx] = gv;
         }
-        for (int t = threadIdx.x; t < nt; t += blockDim.x) {
-            const size_t row = (size_t)(r0 + t0 + t);
-            const float zb = raw_at<TR>(p.b_raw, row * p.ld_b + head);
-            sb[t] = 1.0f / (1.0f + expf(-zb));
-            if (!PER_CHANNEL) {
-                const float z = raw_at<TR>(p.a_raw, row * p.ld_a + head) + dtb.at(head);
-                sg[t] = expf(-rate * softplus_f(z));
+        constexpr int N_V = (SCAN_TOKENS * 32 + STAGE_THREADS - 1) / STAGE_THREADS;     // at most 32 value channels per block
+        float vv[N_V];
+#pragma unroll
+        for (int it = 0; it < N_V; ++it) {
+            const int idx = who + it * STAGE_THREADS;
+            const int t = idx / p.cols, c = idx - t * p.cols;
+            vv[it] = (t < nt && c < n_cols) ? p.qkv[(size_t)(r0 + t0 + t) * channels + 2 * qk + head * p.dv + blockIdx.z * p.cols + c] : 0.f;
+        }
+        float zb = 0.f, za = 0.f;
+        if (who < nt) {
+            const size_t row = (size_t)(r0 + t0 + who);
+            zb = raw_at<TR>(p.b_raw, row * p.ld_b + head);
+            if (!PER_CHANNEL) za = raw_at<TR>(p.a_raw, row * p.ld_a + head);
+        }
+#pragma unroll
+        for (int it = 0; it < N_IT; ++it) {
+            const int idx = who + it * STAGE_THREADS;
+            const int t = idx / DK, i = idx - t * DK;
+            if (t < nt) {
+                sq[idx] = qv[it];
+                sk[idx] = kv[it];
+                if (PER_CHANNEL) sg[idx] = i < p.dk ? expf(-rate * softplus_f(gz[it] + dtb.at(head * p.dk + i))) : 1.f;
             }
         }
 #pragma unroll
-        for (int t = 0; t < SCAN_TOKENS; ++t)
-            if (live_col && t < nt) sv[t * blockDim.x + threadIdx.x] = p.qkv[(size_t)(r0 + t0 + t) * channels + 2 * qk + head * p.dv + col];
-        __syncthreads();
-        if (live_col) {
+        for (int it = 0; it < N_V; ++it) {
+            const int idx = who + it * STAGE_THREADS;
+            if (idx < nt * p.cols) sv[idx] = vv[it];
+        }
+        if (who < nt) {
+            sb[who] = 1.0f / (1.0f + expf(-zb));
+            if (!PER_CHANNEL) sg[who] = expf(-rate * softplus_f(za + dtb.at(head)));
+        }
+    };
+
+    if (!consumer) stage(0, 0, threadIdx.x - walkers);
+    __syncthreads();
+    for (int c = 0; c < chunks; ++c) {
+        const int t0 = c * SCAN_TOKENS, nt = min(SCAN_TOKENS, n - t0);
+        if (!consumer) {
+            if (c + 1 < chunks) stage(t0 + SCAN_TOKENS, (c + 1) & 1, threadIdx.x - walkers);
+        } else {
+            const float* sq = sm + (size_t)(c & 1) * buf_floats;
+            const float* sk = sq + SCAN_TOKENS * DK;
+            const float* sg = sk + SCAN_TOKENS * DK;
+            const float* sb = sg + G_FLOATS;
+            const float* sv = sb + SCAN_TOKENS;
             for (int t = 0; t < nt; ++t) {
-                const float4* q4 = (const float4*)(sq + t * DK);
-                const float4* k4 = (const float4*)(sk + t * DK);
-                const float4* g4 = (const float4*)(sg + t * DK);
+                const float4* q4 = (const float4*)(sq + t * DK) + part;
+                const float4* k4 = (const float4*)(sk + t * DK) + part;
+                const float4* g4 = (const float4*)(sg + t * DK) + part;
                 const float gh = PER_CHANNEL ? 1.f : sg[t];
-                // decay, and what the decayed state holds along the key: four chains
+                // decay, and what the decayed state holds along the key
                 float r = 0.f, r1 = 0.f, r2 = 0.f, r3 = 0.f;
 #pragma unroll
-                for (int i = 0; i < DK / 4; ++i) {
-                    const float4 k = k4[i];
+                for (int m = 0; m < PER / 4; ++m) {
+                    const float4 k = k4[PARTS * m];
                     if (PER_CHANNEL) {
-                        const float4 g = g4[i];
-                        s[4 * i] *= g.x; s[4 * i + 1] *= g.y; s[4 * i + 2] *= g.z; s[4 * i + 3] *= g.w;
+                        const float4 g = g4[PARTS * m];
+                        s[4 * m] *= g.x; s[4 * m + 1] *= g.y; s[4 * m + 2] *= g.z; s[4 * m + 3] *= g.w;
                     } else {
-                        s[4 * i] *= gh; s[4 * i + 1] *= gh; s[4 * i + 2] *= gh; s[4 * i + 3] *= gh;
+                        s[4 * m] *= gh; s[4 * m + 1] *= gh; s[4 * m + 2] *= gh; s[4 * m + 3] *= gh;
                     }
-                    r = fmaf(k.x, s[4 * i], r);
-                    r1 = fmaf(k.y, s[4 * i + 1], r1);
-                    r2 = fmaf(k.z, s[4 * i + 2], r2);
-                    r3 = fmaf(k.w, s[4 * i + 3], r3);
+                    r = fmaf(k.x, s[4 * m], r);
+                    r1 = fmaf(k.y, s[4 * m + 1], r1);
+                    r2 = fmaf(k.z, s[4 * m + 2], r2);
+                    r3 = fmaf(k.w, s[4 * m + 3], r3);
                 }
                 r = (r + r1) + (r2 + r3);
-                const float u = sb[t] * (sv[t * blockDim.x + threadIdx.x] - r);
+                r += __shfl_xor_sync(0xffffffffu, r, 8);
+                r += __shfl_xor_sync(0xffffffffu, r, 16);
+                const float u = sb[t] * (sv[t * p.cols + local_col] - r);
                 float o = 0.f, o1 = 0.f, o2 = 0.f, o3 = 0.f;
 #pragma unroll
-                for (int i = 0; i < DK / 4; ++i) {
-                    const float4 k = k4[i], q = q4[i];
-                    s[4 * i] = fmaf(k.x, u, s[4 * i]);         o = fmaf(q.x, s[4 * i], o);
-                    s[4 * i + 1] = fmaf(k.y, u, s[4 * i + 1]); o1 = fmaf(q.y, s[4 * i + 1], o1);
-                    s[4 * i + 2] = fmaf(k.z, u, s[4 * i + 2]); o2 = fmaf(q.z, s[4 * i + 2], o2);
-                    s[4 * i + 3] = fmaf(k.w, u, s[4 * i + 3]); o3 = fmaf(q.w, s[4 * i + 3], o3);
+                for (int m = 0; m < PER / 4; ++m) {
+                    const float4 k = k4[PARTS * m], q = q4[PARTS * m];
+                    s[4 * m] = fmaf(k.x, u, s[4 * m]);         o = fmaf(q.x, s[4 * m], o);
+                    s[4 * m + 1] = fmaf(k.y, u, s[4 * m + 1]); o1 = fmaf(q.y, s[4 * m + 1], o1);
+                    s[4 * m + 2] = fmaf(k.z, u, s[4 * m + 2]); o2 = fmaf(q.z, s[4 * m + 2], o2);
+                    s[4 * m + 3] = fmaf(k.w, u, s[4 * m + 3]); o3 = fmaf(q.w, s[4 * m + 3], o3);
                 }
-                p.out[(size_t)(r0 + t0 + t) * ((size_t)p.heads * p.dv) + head * p.dv + col] = (o + o1) + (o2 + o3);
+                o = (o + o1) + (o2 + o3);
+                o += __shfl_xor_sync(0xffffffffu, o, 8);
+                o += __shfl_xor_sync(0xffffffffu, o, 16);
+                if (part == 0 && live_col) p.out[(size_t)(r0 + t0 + t) * ((size_t)p.heads * p.dv) + head * p.dv + col] = o;
             }
         }
+        __syncthreads();
     }
     if (live_col) {
 #pragma unroll
-        for (int i = 0; i < DK; ++i)
-            if (i < p.dk) S[(size_t)i * p.dv + col] = s[i];
+        for (int j = 0; j < PER; ++j) {
+            const int i = 4 * (PARTS * (j >> 2) + part) + (j & 3);
+            if (i < p.dk) S[(size_t)i * p.dv + col] = s[j];
+        }
     }
 }
 
 template <typename TR, int DK>
-int launch_scan(const ScanArgs& p, int n_seqs, int splits, int threads, cudaStream_t stream) {
+int launch_scan(const ScanArgs& p, int n_seqs, int splits, cudaStream_t stream) {
     const size_t floats = (size_t)2 * SCAN_TOKENS * DK + (p.per_channel ? (size_t)SCAN_TOKENS * DK : SCAN_TOKENS) + SCAN_TOKENS +
-                          (size_t)SCAN_TOKENS * threads;
-    const size_t smem = floats * sizeof(float);
+                          (size_t)SCAN_TOKENS * p.cols;
+    const size_t smem = 2 * floats * sizeof(float);
     const dim3 grid(n_seqs, p.heads, splits);
-    if (p.per_channel) FR_CUDA(fr_launch(delta_scan_kernel<TR, DK, true>, grid, dim3(threads), smem, stream, p));
-    else FR_CUDA(fr_launch(delta_scan_kernel<TR, DK, false>, grid, dim3(threads), smem, stream, p));
+    const dim3 block(PARTS * p.cols + STAGE_THREADS);
+    if (p.per_channel) {
+        if (smem > 48 * 1024) FR_CUDA(cudaFuncSetAttribute(delta_scan_kernel<TR, DK, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+        FR_CUDA(fr_launch(delta_scan_kernel<TR, DK, true>, grid, block, smem, stream, p));
+    } else {
+        if (smem > 48 * 1024) FR_CUDA(cudaFuncSetAttribute(delta_scan_kernel<TR, DK, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+        FR_CUDA(fr_launch(delta_scan_kernel<TR, DK, false>, grid, block, smem, stream, p));
+    }
     FR_CHECK_LAUNCH("delta scan");
     return FR_OK;
 }
 
 template <typename TR>
-int scan_by_size(const ScanArgs& p, int n_seqs, int splits, int threads, cudaStream_t stream) {
-    if (p.dk <= 16) return launch_scan<TR, 16>(p, n_seqs, splits, threads, stream);
-    if (p.dk <= 32) return launch_scan<TR, 32>(p, n_seqs, splits, threads, stream);
-    if (p.dk <= 64) return launch_scan<TR, 64>(p, n_seqs, splits, threads, stream);
-    if (p.dk <= 128) return launch_scan<TR, 128>(p, n_seqs, splits, threads, stream);
-    if (p.dk <= 256) return launch_scan<TR, 256>(p, n_seqs, splits, threads, stream);
+int scan_by_size(const ScanArgs& p, int n_seqs, int splits, cudaStream_t stream) {
+    if (p.dk <= 16) return launch_scan<TR, 16>(p, n_seqs, splits, stream);
+    if (p.dk <= 32) return launch_scan<TR, 32>(p, n_seqs, splits, stream);
+    if (p.dk <= 64) return launch_scan<TR, 64>(p, n_seqs, splits, stream);
+    if (p.dk <= 128) return launch_scan<TR, 128>(p, n_seqs, splits, stream);
+    if (p.dk <= 256) return launch_scan<TR, 256>(p, n_seqs, splits, stream);
     FR_REFUSE("delta scan: %d key channels per head (at most 256)", p.dk);
 }
 
@@ -345,15 +414,14 @@ FR_EXPORT int delta_scan(const float* qkv, const void* a_raw, int ld_a, const vo
     p.out = out; p.state = state; p.state_stride = state_stride; p.s_off = s_off; p.row_seq = row_seq; p.seq_start = seq_start;
     p.seq_qlen = seq_qlen; p.seq_slots = seq_slots; p.ld_a = ld_a; p.ld_b = ld_b; p.heads = heads; p.qk_heads = qk_heads; p.dk = dk;
     p.dv = dv; p.per_channel = per_channel ? 1 : 0;
-    // value channels per block: 32 where the device would otherwise stay empty, up to 128
+    // value channels per block (four threads each): 32, or 16 where the device would otherwise stay empty
     const int sms = fr_sm_count() > 0 ? fr_sm_count() : 128;
-    int cols = 128;
-    while (cols > 32 && (long long)n_seqs * heads * ((dv + cols - 1) / cols) < 2LL * sms) cols >>= 1;
-    if (cols > ((dv + 31) / 32) * 32) cols = ((dv + 31) / 32) * 32;
+    int cols = 32;
+    if ((long long)n_seqs * heads * ((dv + cols - 1) / cols) < 2LL * sms) cols = 16;
+    if (cols > ((dv + 7) / 8) * 8) cols = ((dv + 7) / 8) * 8;
     p.cols = cols;
     const int splits = (dv + cols - 1) / cols;
-    const int threads = cols < 64 ? 64 : cols;
-    if (raw_dtype == FR_F32) return scan_by_size<float>(p, n_seqs, splits, threads, stream);
-    if (raw_dtype == FR_BF16) return scan_by_size<bf16>(p, n_seqs, splits, threads, stream);
+    if (raw_dtype == FR_F32) return scan_by_size<float>(p, n_seqs, splits, stream);
+    if (raw_dtype == FR_BF16) return scan_by_size<bf16>(p, n_seqs, splits, stream);
     FR_REFUSE("delta scan: unknown dtype %d", raw_dtype);
 }

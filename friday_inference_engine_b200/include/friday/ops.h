@@ -188,6 +188,12 @@ public:
     // gate (null: none): the result is multiplied by sigmoid(gate[row][gate_off + h]); out: head h at h * out_stride
     void head_linear(const Tensor& x, int64_t x_off, int64_t x_stride, const Tensor& w, bool per_head_rows_k, Tensor& out,
                      int64_t out_stride, const Tensor* gate, int64_t gate_off, int heads, int k, int n, const StepContext& ctx);
+    // Prompts in bfloat16: the same attention as products on the tensor cores, sequence by sequence and head by head, with keys
+    // and values expanded from the gathered latents: scores = Qn Kn^T + Qr R^T (fp32), a masked softmax with the sink whose
+    // weights are kept as two bf16 numbers each, result = P V.  `proj` holds the queries with their rotated parts already
+    // rotated; the step's rows are in the cache.  Returns [rows, heads * vdim] in proj's dtype, gates applied.
+    Tensor latent_attention_prompt(const Tensor& proj, const Tensor& w_uk, const Tensor& w_uv, const Tensor* sink, const LatentSpec& spec,
+                                   const CacheView& view, const StepContext& ctx);
     // qf [rows, heads * (rank + rot)] fp32 against the cached [latent | key part] rows -> [rows, heads * rank] fp32
     Tensor latent_attention(const Tensor& qf, const Tensor* sink, const LatentSpec& spec, const CacheView& view, const StepContext& ctx);
 

@@ -98,6 +98,9 @@ struct AttentionLatent {
                        int, int, int, int, cudaStream_t);
     int (*run)(const float*, float*, const void*, const void*, const int*, int, int, const int*, const int*, const void*, int, int,
                int, int, int, float, int, float*, int, cudaStream_t);
+    int (*gather)(const void*, const void*, const int*, int, int, int, int, int, void*, void*, int, cudaStream_t);
+    int (*softmax_split)(const float*, int, int, int, int, float, const void*, int, int, void*, void*, cudaStream_t);
+    int (*gate_cast)(const float*, const void*, int, int, int, int, int, void*, int, cudaStream_t);
 };
 struct Routed {
     last_error_fn last_error;

@@ -227,7 +227,8 @@ Tensor Ops::add_scaled(const Tensor& residual, const Tensor& y, float alpha, con
 Tensor Ops::linear_residual(const Rows& x, const Tensor& weight, const Tensor* bias, const Tensor& residual, float alpha) {
     if (alpha == 1.0f && residual.dtype == x.t.dtype) return linear(x, weight, bias, &residual);
     if (residual.dtype != DType::F32) throw KernelError("linear_residual: a multiplier needs a 32-bit residual stream");
-    if (alpha == 1.0f && x.t.dtype == DType::F32) return linear(x, weight, bias, &residual, (int)DType::F32);
+    // a 32-bit stream takes the product's 32-bit sums in the product's own epilogue, whatever the activations' dtype
+    if (alpha == 1.0f) return linear(x, weight, bias, &residual, (int)DType::F32);
     Tensor y = linear(x, weight, bias, nullptr, (int)DType::F32);
     return add_scaled(residual, y, alpha);
 }
@@ -456,6 +457,60 @@ Tensor Ops::latent_attention(const Tensor& qf, const Tensor* sink, const LatentS
                              view.page_size, ctx.row_seq, ctx.row_pos, sink ? sink->data : nullptr, sink ? code(sink->dtype) : 0, rows,
                              s.heads, s.rank, s.rot, s.scale, splits, scratch, code(view.dtype), stream_), "attention_latent");
     if (splits > 1) ++launches_;
+    return out;
+}
+
+Tensor Ops::latent_attention_prompt(const Tensor& proj, const Tensor& w_uk, const Tensor& w_uv, const Tensor* sink, const LatentSpec& s,
+                                    const CacheView& view, const StepContext& ctx) {
+    if (view.kind != CacheRequest::KV || !view.k_pool) throw KernelError("latent_attention needs a view of cached rows");
+    if (proj.dtype != DType::BF16 || view.dtype != DType::BF16 || (int)ctx.q_lens.size() != ctx.n_seqs || (int)ctx.kv_lens.size() != ctx.n_seqs)
+        throw KernelError("latent_attention_prompt: bfloat16 rows and a step whose lengths the host knows");
+    const auto& k = kernels::attention_latent();
+    const int64_t hv = (int64_t)s.heads * s.vdim;
+    Tensor of = alloc(DType::F32, proj.rows(), hv);
+    int64_t r0 = 0;
+    for (int q = 0; q < ctx.n_seqs; ++q) {
+        const int64_t T = ctx.q_lens[(size_t)q], n = ctx.kv_lens[(size_t)q], n_pad = (n + 7) / 8 * 8;
+        if (T <= 0) continue;
+        Tensor c_all = alloc(DType::BF16, n_pad, s.rank), r_all = alloc(DType::BF16, n_pad, s.rot);
+        {
+            Timed t(*this, Attention);
+            call(launches_, k, k.gather(view.k_pool, view.v_pool, view.block_table + (size_t)q * view.table_width, view.page_size, (int)n,
+                                        (int)n_pad, s.rank, s.rot, c_all.data, r_all.data, code(DType::BF16), stream_), "latent gather");
+        }
+        Tensor kn = linear(Rows(c_all), w_uk);                     // [n_pad, heads * dim]: every head's unrotated keys
+        Tensor vt = linear(Rows(w_uv), c_all);                     // [heads * vdim, n_pad]: every head's values, transposed
+        Tensor scores = alloc(DType::F32, T, n_pad);
+        Tensor p_hi = alloc(DType::BF16, T, n_pad), p_lo = alloc(DType::BF16, T, n_pad);
+        const Tensor rows = proj.row_slice(r0, T);
+        for (int h = 0; h < s.heads; ++h) {
+            Tensor qn = rows, qr = rows, kh = kn, vh = vt.row_slice((int64_t)h * s.vdim, s.vdim);
+            qn.data = (char*)rows.data + (size_t)(s.q_off + (int64_t)h * (s.dim + s.rot)) * 2;
+            qn.shape[1] = s.dim;
+            qr.data = (char*)qn.data + (size_t)s.dim * 2;
+            qr.shape[1] = s.rot;
+            kh.data = (char*)kn.data + (size_t)h * s.dim * 2;
+            kh.shape[1] = s.dim;
+            linear(Rows(qn), kh, nullptr, nullptr, (int)DType::F32, &scores);
+            linear(Rows(qr), r_all, nullptr, &scores, (int)DType::F32, &scores);
+            {
+                Timed t(*this, Attention);
+                call(launches_, k, k.softmax_split((const float*)scores.data, (int)scores.ld, (int)T, (int)n_pad, (int)(n - T), s.scale,
+                                                   sink ? sink->data : nullptr, sink ? code(sink->dtype) : 0, h, p_hi.data, p_lo.data,
+                                                   stream_), "softmax_split");
+            }
+            Tensor oh = of.row_slice(r0, T);
+            oh.data = (char*)oh.data + (size_t)h * s.vdim * 4;
+            oh.shape[1] = s.vdim;
+            linear(Rows(p_hi), vh, nullptr, nullptr, (int)DType::F32, &oh);
+            linear(Rows(p_lo), vh, nullptr, &oh, (int)DType::F32, &oh);
+        }
+        r0 += T;
+    }
+    Tensor out = alloc(proj.dtype, proj.rows(), hv);
+    Timed t(*this, Other);
+    call(launches_, k, k.gate_cast((const float*)of.data, s.gate_off >= 0 ? proj.data : nullptr, (int)proj.ld, (int)s.gate_off,
+                                   (int)proj.rows(), s.heads, s.vdim, out.data, code(proj.dtype), stream_), "gate_cast");
     return out;
 }
 

@@ -17,6 +17,7 @@
 // The states, decays, betas, unit norms, scores and weights are fp32 (csrc/delta.cu, csrc/attention_latent.cu).  Every
 // part adds into the residual stream that it is given, in that stream's dtype.
 #include <math.h>
+#include <stdlib.h>
 
 #include <string>
 
@@ -201,6 +202,14 @@ public:
         Tensor qf = ops.alloc(DType::F32, x.rows(), (int64_t)heads_ * kvd);
         Tensor ckr = ops.latent_prepare(in, tensor("dkv.norm"), sp, qf, ctx);
         ops.kv_store(ckr, 0, rank_, view, ctx);
+        // prompts in bfloat16: keys and values expanded per head, products on the tensor cores (FRIDAY_LATENT_TC=0: never)
+        const char* tc = getenv("FRIDAY_LATENT_TC");
+        if (x.dtype == DType::BF16 && view.dtype == DType::BF16 && !ctx.decode && ctx.max_q_len >= 32 && (int)ctx.q_lens.size() == ctx.n_seqs &&
+            dim_ % 8 == 0 && rot_ % 8 == 0 && vdim_ % 8 == 0 && rank_ % 8 == 0 && !(tc && tc[0] == '0')) {
+            ops.rotate_pairs(in, ctx, freq_, mult_, heads_, dim_ + rot_, dim_, rot_);
+            Tensor mixed = ops.latent_attention_prompt(in, tensor("uk"), tensor("uv"), has_sink_ ? &tensor("sink") : nullptr, sp, view, ctx);
+            return PartOut(ops.linear_residual(Rows(mixed), tensor("o"), nullptr, residual, out_scale));
+        }
         ops.head_linear(in, 0, dim_ + rot_, tensor("uk"), true, qf, kvd, nullptr, 0, heads_, dim_, rank_, ctx);
         Tensor lat = ops.latent_attention(qf, has_sink_ ? &tensor("sink") : nullptr, sp, view, ctx);
         // values: W_uv,h times the head's weighted latent, times the head's gate

@@ -255,7 +255,22 @@ struct AttnArgs {
     float scale;
 };
 
-template <typename T>
+// V numbers per lane and load: lane l owns dimensions V l + e + 32 V i (e < V).  V = 2 needs an even latent size and an
+// even rotated part (rows of the pools then start on 4-byte boundaries).
+template <typename T, int V> struct Pack;
+template <> struct Pack<float, 1> { static __device__ __forceinline__ void load(const float* p, float* o) { o[0] = *p; } };
+template <> struct Pack<bf16, 1> { static __device__ __forceinline__ void load(const bf16* p, float* o) { o[0] = __bfloat162float(*p); } };
+template <> struct Pack<float, 2> {
+    static __device__ __forceinline__ void load(const float* p, float* o) { const float2 v = *(const float2*)p; o[0] = v.x; o[1] = v.y; }
+};
+template <> struct Pack<bf16, 2> {
+    static __device__ __forceinline__ void load(const bf16* p, float* o) {
+        const float2 v = __bfloat1622float2(*(const __nv_bfloat162*)p);
+        o[0] = v.x; o[1] = v.y;
+    }
+};
+
+template <typename T, int V>
 __global__ void __launch_bounds__(128) latent_attention_kernel(AttnArgs p) {
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int item = blockIdx.x * 4 + warp;          // (row, head)
@@ -265,6 +280,7 @@ __global__ void __launch_bounds__(128) latent_attention_kernel(AttnArgs p) {
     fr_pdl_wait();
     fr_pdl_launch();
     const int seq = p.row_seq[row];
+    constexpr int CI = C_PER_LANE / V, RI = R_PER_LANE / V;
     float qc[C_PER_LANE], qr[R_PER_LANE], acc[C_PER_LANE];
 #pragma unroll
     for (int i = 0; i < C_PER_LANE; ++i) acc[i] = 0.f;
@@ -275,15 +291,19 @@ __global__ void __launch_bounds__(128) latent_attention_kernel(AttnArgs p) {
         const int i0 = split * chunk, i1 = min(i0 + chunk, n);
         const float* q = p.q + (size_t)item * (p.rank + p.rot);
 #pragma unroll
-        for (int i = 0; i < C_PER_LANE; ++i) {
-            const int d = lane + 32 * i;
-            qc[i] = d < p.rank ? q[d] * p.scale : 0.f;
-        }
+        for (int i = 0; i < CI; ++i)
 #pragma unroll
-        for (int i = 0; i < R_PER_LANE; ++i) {
-            const int d = lane + 32 * i;
-            qr[i] = d < p.rot ? q[p.rank + d] * p.scale : 0.f;
-        }
+            for (int e = 0; e < V; ++e) {
+                const int d = V * lane + 32 * V * i + e;
+                qc[V * i + e] = d < p.rank ? q[d] * p.scale : 0.f;
+            }
+#pragma unroll
+        for (int i = 0; i < RI; ++i)
+#pragma unroll
+            for (int e = 0; e < V; ++e) {
+                const int d = V * lane + 32 * V * i + e;
+                qr[V * i + e] = d < p.rot ? q[p.rank + d] * p.scale : 0.f;
+            }
         const int* table = p.block_table + (size_t)seq * p.table_width;
         // two keys at a time: their loads are issued together
         for (int j = i0; j < i1; j += 2) {
@@ -296,15 +316,23 @@ __global__ void __launch_bounds__(128) latent_attention_kernel(AttnArgs p) {
                 const T* rr = (const T*)p.r_pool + at * p.rot;
                 float s = 0.f;
 #pragma unroll
-                for (int i = 0; i < C_PER_LANE; ++i) {
-                    const int d = lane + 32 * i;
-                    cv[u][i] = d < p.rank ? fr_load(cr + d) : 0.f;
-                    s = fmaf(qc[i], cv[u][i], s);
+                for (int i = 0; i < CI; ++i) {
+                    const int d = V * lane + 32 * V * i;
+#pragma unroll
+                    for (int e = 0; e < V; ++e) cv[u][V * i + e] = 0.f;
+                    if (d < p.rank) Pack<T, V>::load(cr + d, &cv[u][V * i]);
+#pragma unroll
+                    for (int e = 0; e < V; ++e) s = fmaf(qc[V * i + e], cv[u][V * i + e], s);
                 }
 #pragma unroll
-                for (int i = 0; i < R_PER_LANE; ++i) {
-                    const int d = lane + 32 * i;
-                    if (d < p.rot) s = fmaf(qr[i], fr_load(rr + d), s);
+                for (int i = 0; i < RI; ++i) {
+                    const int d = V * lane + 32 * V * i;
+                    float rv[V];
+#pragma unroll
+                    for (int e = 0; e < V; ++e) rv[e] = 0.f;
+                    if (d < p.rot) Pack<T, V>::load(rr + d, rv);
+#pragma unroll
+                    for (int e = 0; e < V; ++e) s = fmaf(qr[V * i + e], rv[e], s);
                 }
                 s2[u] = s;
             }
@@ -326,10 +354,12 @@ __global__ void __launch_bounds__(128) latent_attention_kernel(AttnArgs p) {
     if (p.splits > 1) {
         float* part = p.part + ((size_t)item * p.splits + split) * (p.rank + 2);
 #pragma unroll
-        for (int i = 0; i < C_PER_LANE; ++i) {
-            const int d = lane + 32 * i;
-            if (d < p.rank) part[d] = acc[i];
-        }
+        for (int i = 0; i < CI; ++i)
+#pragma unroll
+            for (int e = 0; e < V; ++e) {
+                const int d = V * lane + 32 * V * i + e;
+                if (d < p.rank) part[d] = acc[V * i + e];
+            }
         if (lane == 0) {
             part[p.rank] = m;
             part[p.rank + 1] = l;
@@ -347,10 +377,12 @@ __global__ void __launch_bounds__(128) latent_attention_kernel(AttnArgs p) {
     }
     const float inv = denom > 0.f ? f / denom : 0.f;
 #pragma unroll
-    for (int i = 0; i < C_PER_LANE; ++i) {
-        const int d = lane + 32 * i;
-        if (d < p.rank) o[d] = acc[i] * inv;
-    }
+    for (int i = 0; i < CI; ++i)
+#pragma unroll
+        for (int e = 0; e < V; ++e) {
+            const int d = V * lane + 32 * V * i + e;
+            if (d < p.rank) o[d] = acc[V * i + e] * inv;
+        }
 }
 
 __global__ void __launch_bounds__(128) latent_merge_kernel(AttnArgs p) {
@@ -361,23 +393,29 @@ __global__ void __launch_bounds__(128) latent_merge_kernel(AttnArgs p) {
     if (item >= p.rows * p.heads) return;
     const int h = item % p.heads;
     const float* part = p.part + (size_t)item * p.splits * (p.rank + 2);
+    // every lane takes the maximum and the sum of some splits: their loads are in flight together
     float top = -INFINITY;
-    for (int s = 0; s < p.splits; ++s) top = fmaxf(top, part[(size_t)s * (p.rank + 2) + p.rank]);
+    for (int s = lane; s < p.splits; s += 32) top = fmaxf(top, part[(size_t)s * (p.rank + 2) + p.rank]);
+    top = fr_warp_max(top);
     const bool live = p.row_seq[item / p.heads] >= 0;
     float sk = -INFINITY;
     if (p.sink != nullptr && live) {
         sk = FrVec{p.sink, p.sink_dtype}.at(h);
         top = fmaxf(top, sk);
     }
-    float l = 0.f, acc[C_PER_LANE];
+    float l = 0.f;
+    for (int s = lane; s < p.splits; s += 32) {
+        const float ls = part[(size_t)s * (p.rank + 2) + p.rank + 1];
+        if (ls > 0.f) l += ls * expf(part[(size_t)s * (p.rank + 2) + p.rank] - top);
+    }
+    l = fr_warp_sum(l);
+    float acc[C_PER_LANE];
 #pragma unroll
     for (int i = 0; i < C_PER_LANE; ++i) acc[i] = 0.f;
     for (int s = 0; s < p.splits; ++s) {
         const float* ps = part + (size_t)s * (p.rank + 2);
         const float ls = ps[p.rank + 1];
-        if (!(ls > 0.f)) continue;
-        const float f = expf(ps[p.rank] - top);
-        l += ls * f;
+        const float f = ls > 0.f ? expf(ps[p.rank] - top) : 0.f;
 #pragma unroll
         for (int i = 0; i < C_PER_LANE; ++i) {
             const int d = lane + 32 * i;
@@ -540,8 +578,11 @@ FR_EXPORT int attention_latent(const float* q, float* out, const void* c_pool, c
                rot, splits, scale};
     const int items = rows * heads;
     const dim3 grid((items + 3) / 4, splits);
-    if (dtype == FR_F32) FR_CUDA(fr_launch(latent_attention_kernel<float>, grid, dim3(128), 0, stream, p));
-    else if (dtype == FR_BF16) FR_CUDA(fr_launch(latent_attention_kernel<bf16>, grid, dim3(128), 0, stream, p));
+    const bool pairs = rank % 2 == 0 && rot % 2 == 0 && (((uintptr_t)c_pool | (uintptr_t)r_pool) & 7) == 0;
+    if (dtype == FR_F32 && pairs) FR_CUDA(fr_launch(latent_attention_kernel<float, 2>, grid, dim3(128), 0, stream, p));
+    else if (dtype == FR_F32) FR_CUDA(fr_launch(latent_attention_kernel<float, 1>, grid, dim3(128), 0, stream, p));
+    else if (dtype == FR_BF16 && pairs) FR_CUDA(fr_launch(latent_attention_kernel<bf16, 2>, grid, dim3(128), 0, stream, p));
+    else if (dtype == FR_BF16) FR_CUDA(fr_launch(latent_attention_kernel<bf16, 1>, grid, dim3(128), 0, stream, p));
     else FR_REFUSE("latent attention: unknown dtype %d", dtype);
     FR_CHECK_LAUNCH("latent attention");
     if (splits > 1) {

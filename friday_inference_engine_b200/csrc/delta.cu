@@ -13,8 +13,8 @@
 //                  the sequence's state, zeros at a sequence's start), then silu; every q and k head is made a unit
 //                  vector x / sqrt(sum x^2 + unit_eps), q is multiplied by q_scale.  Results are fp32.
 //   conv_state     the last taps-1 inputs of every sequence become its state's history (after conv_prepare has read it)
-//   scan           the recurrence, per (sequence, head): four threads share one value channel (a column of S, a quarter of its
-//                  dk numbers in each thread's registers); other warps of the block stage the next eight tokens through shared
+//   scan           the recurrence, per (sequence, head): up to sixteen threads share one value channel (a column of S, each
+//                  with its share of the dk numbers in registers); other warps of the block stage the next eight tokens through shared
 //                  memory meanwhile.  beta = sigmoid(raw),
 //                  g = exp(-exp(A_log) * softplus(raw + dt_bias)) are formed here in fp32.  Columns of S never mix, so
 //                  any split of the value channels over blocks is exact.
@@ -46,6 +46,7 @@ struct ConvArgs {
     const int* seq_slots;
     int ld, q_off, k_off, v_off, qk_heads, dk, v_channels, taps, rows;
     float q_scale, unit_eps;
+    int shift;                // 1: every sequence brings one row, and the thread that convolves a channel moves its history on
 };
 
 __device__ __forceinline__ float silu_f(float z) { return z / (1.0f + expf(-z)); }
@@ -63,6 +64,18 @@ __device__ __forceinline__ float conv_at(const ConvArgs& p, const T* x, int src_
         if (r >= r0) in = fr_load(x + (size_t)r * p.ld + src_col);
         else in = hist[(size_t)(p.taps - 1 + (r - r0)) * channels + c];
         acc = fmaf(w.at(c * p.taps + j), in, acc);
+    }
+    if (p.shift) {
+        // one row per sequence: nobody else reads or writes this channel's history, so it moves on here
+        float* h = const_cast<float*>(hist);
+        const int keep = p.taps - 1;
+        float next[MAX_TAPS];
+#pragma unroll
+        for (int j = 0; j < MAX_TAPS; ++j)
+            if (j < keep) next[j] = j + 1 < keep ? h[(size_t)(j + 1) * channels + c] : fr_load(x + (size_t)row * p.ld + src_col);
+#pragma unroll
+        for (int j = 0; j < MAX_TAPS; ++j)
+            if (j < keep) h[(size_t)j * channels + c] = next[j];
     }
     return silu_f(acc);
 }
@@ -82,7 +95,8 @@ __global__ void __launch_bounds__(256) conv_prepare_kernel(ConvArgs p) {
     const T* x = (const T*)p.x;
     float* out = p.out + (size_t)row * channels;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, warps = blockDim.x >> 5;
-    for (int item = warp; item < 2 * p.qk_heads; item += warps) {
+    // few rows: the heads and value channels of a row are spread over gridDim.y blocks
+    for (int item = blockIdx.y * warps + warp; item < 2 * p.qk_heads; item += gridDim.y * warps) {
         const bool is_q = item < p.qk_heads;
         const int head = is_q ? item : item - p.qk_heads;
         const int c0 = item * p.dk;                                  // channel index in q|k|v order
@@ -106,7 +120,7 @@ __global__ void __launch_bounds__(256) conv_prepare_kernel(ConvArgs p) {
             if (d < p.dk) out[c0 + d] = vals[i] * inv;
         }
     }
-    for (int d = threadIdx.x; d < p.v_channels; d += blockDim.x)
+    for (int d = blockIdx.y * blockDim.x + threadIdx.x; d < p.v_channels; d += gridDim.y * blockDim.x)
         out[2 * qk + d] = conv_at(p, x, p.v_off + d, 2 * qk + d, row, r0, hist, channels);
 }
 
@@ -164,25 +178,28 @@ template <typename TR>
 __device__ __forceinline__ float raw_at(const void* p, size_t i) { return fr_load((const TR*)p + i); }
 
 constexpr int STAGE_THREADS = 128;   // warps that only stage tokens, beside the warps that own value channels
-constexpr int PARTS = 4;             // threads that share a value channel: each owns a quarter of the key channels
+// Threads that share a value channel, each with its share of the key channels in registers.  Four: with sixteen (eight
+// numbers of 128 per thread, four shuffles per sum) a prompt's scan took as long and a one-token step longer.
+constexpr int parts_of(int) { return 4; }
 
-// The first PARTS * p.cols threads walk the tokens: lanes (part, channel) of a warp own 8 value channels, four lanes each,
-// with the key channels dealt out in groups of four (part p owns groups p, p + 4, ...: neighbouring lanes read neighbouring
-// 16-byte pieces of shared memory); what the state holds along the key, and the read-out, are summed over the four lanes
-// with two shuffles.  The other STAGE_THREADS threads stage the next SCAN_TOKENS tokens (q, k, decays, betas, values) into
+// The first PARTS * p.cols threads walk the tokens: lanes (part, channel) of a warp own 32 / PARTS value channels, PARTS
+// lanes each, with the key channels dealt out in groups of four (part p owns groups p, p + PARTS, ...: neighbouring lanes
+// read neighbouring 16-byte pieces of shared memory); what the state holds along the key, and the read-out, are summed
+// over the PARTS lanes with shuffles.  The other STAGE_THREADS threads stage the next SCAN_TOKENS tokens (q, k, decays, betas, values) into
 // the other half of shared memory meanwhile, so that the chain never waits for global memory.  One barrier per SCAN_TOKENS
 // tokens.
 template <typename TR, int DK, bool PER_CHANNEL>
 __global__ void delta_scan_kernel(ScanArgs p) {
     extern __shared__ float sm[];
     constexpr int G_FLOATS = PER_CHANNEL ? SCAN_TOKENS * DK : SCAN_TOKENS;
+    constexpr int PARTS = parts_of(DK), CPW = 32 / PARTS;      // lanes per value channel, value channels per warp
     constexpr int PER = DK / PARTS;                   // key channels per thread
     const int buf_floats = 2 * SCAN_TOKENS * DK + G_FLOATS + SCAN_TOKENS + SCAN_TOKENS * p.cols;
     const int seq = blockIdx.x, head = blockIdx.y;
     const int walkers = PARTS * p.cols;
     const bool consumer = (int)threadIdx.x < walkers;
-    const int lane = threadIdx.x & 31, part = lane >> 3;
-    const int local_col = (threadIdx.x >> 5) * 8 + (lane & 7);
+    const int lane = threadIdx.x & 31, part = lane / CPW;
+    const int local_col = (threadIdx.x >> 5) * CPW + (lane % CPW);
     const int col = blockIdx.z * p.cols + local_col;
     const bool live_col = consumer && col < p.dv;
     const int r0 = p.seq_start[seq], n = p.seq_qlen[seq];
@@ -273,16 +290,18 @@ __global__ void delta_scan_kernel(ScanArgs p) {
             const float* sg = sk + SCAN_TOKENS * DK;
             const float* sb = sg + G_FLOATS;
             const float* sv = sb + SCAN_TOKENS;
-            for (int t = 0; t < nt; ++t) {
+            // one token: the state decays, is corrected along the key, and is read; returns this thread's channel of the result
+            auto token = [&](int t) {
                 const float4* q4 = (const float4*)(sq + t * DK) + part;
                 const float4* k4 = (const float4*)(sk + t * DK) + part;
                 const float4* g4 = (const float4*)(sg + t * DK) + part;
                 const float gh = PER_CHANNEL ? 1.f : sg[t];
-                // decay, and what the decayed state holds along the key
+                float4 kk[PER / 4];
                 float r = 0.f, r1 = 0.f, r2 = 0.f, r3 = 0.f;
 #pragma unroll
                 for (int m = 0; m < PER / 4; ++m) {
                     const float4 k = k4[PARTS * m];
+                    kk[m] = k;
                     if (PER_CHANNEL) {
                         const float4 g = g4[PARTS * m];
                         s[4 * m] *= g.x; s[4 * m + 1] *= g.y; s[4 * m + 2] *= g.z; s[4 * m + 3] *= g.w;
@@ -295,22 +314,40 @@ __global__ void delta_scan_kernel(ScanArgs p) {
                     r3 = fmaf(k.w, s[4 * m + 3], r3);
                 }
                 r = (r + r1) + (r2 + r3);
-                r += __shfl_xor_sync(0xffffffffu, r, 8);
-                r += __shfl_xor_sync(0xffffffffu, r, 16);
+#pragma unroll
+                for (int w = CPW; w < 32; w <<= 1) r += __shfl_xor_sync(0xffffffffu, r, w);
                 const float u = sb[t] * (sv[t * p.cols + local_col] - r);
                 float o = 0.f, o1 = 0.f, o2 = 0.f, o3 = 0.f;
 #pragma unroll
                 for (int m = 0; m < PER / 4; ++m) {
-                    const float4 k = k4[PARTS * m], q = q4[PARTS * m];
+                    const float4 k = kk[m], q = q4[PARTS * m];
                     s[4 * m] = fmaf(k.x, u, s[4 * m]);         o = fmaf(q.x, s[4 * m], o);
                     s[4 * m + 1] = fmaf(k.y, u, s[4 * m + 1]); o1 = fmaf(q.y, s[4 * m + 1], o1);
                     s[4 * m + 2] = fmaf(k.z, u, s[4 * m + 2]); o2 = fmaf(q.z, s[4 * m + 2], o2);
                     s[4 * m + 3] = fmaf(k.w, u, s[4 * m + 3]); o3 = fmaf(q.w, s[4 * m + 3], o3);
                 }
                 o = (o + o1) + (o2 + o3);
-                o += __shfl_xor_sync(0xffffffffu, o, 8);
-                o += __shfl_xor_sync(0xffffffffu, o, 16);
-                if (part == 0 && live_col) p.out[(size_t)(r0 + t0 + t) * ((size_t)p.heads * p.dv) + head * p.dv + col] = o;
+#pragma unroll
+                for (int w = CPW; w < 32; w <<= 1) o += __shfl_xor_sync(0xffffffffu, o, w);
+                return o;
+            };
+            float* out_at = p.out + (size_t)(r0 + t0) * ((size_t)p.heads * p.dv) + head * p.dv + col;
+            if (DK <= 128) {
+                // the chunk's tokens unrolled, their results kept in registers and stored at the end: a token's read-out
+                // (its sums over the lanes, its store) overlaps the next token's chain, and the loads from shared memory
+                // run ahead (a store in between would hold them back)
+                float res[SCAN_TOKENS];
+#pragma unroll
+                for (int t = 0; t < SCAN_TOKENS; ++t)
+                    if (t < nt) res[t] = token(t);
+#pragma unroll
+                for (int t = 0; t < SCAN_TOKENS; ++t)
+                    if (t < nt && part == 0 && live_col) out_at[(size_t)t * p.heads * p.dv] = res[t];
+            } else {
+                for (int t = 0; t < nt; ++t) {
+                    const float o = token(t);
+                    if (part == 0 && live_col) out_at[(size_t)t * p.heads * p.dv] = o;
+                }
             }
         }
         __syncthreads();
@@ -330,7 +367,7 @@ int launch_scan(const ScanArgs& p, int n_seqs, int splits, cudaStream_t stream) 
                           (size_t)SCAN_TOKENS * p.cols;
     const size_t smem = 2 * floats * sizeof(float);
     const dim3 grid(n_seqs, p.heads, splits);
-    const dim3 block(PARTS * p.cols + STAGE_THREADS);
+    const dim3 block(parts_of(DK) * p.cols + STAGE_THREADS);
     if (p.per_channel) {
         if (smem > 48 * 1024) FR_CUDA(cudaFuncSetAttribute(delta_scan_kernel<TR, DK, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
         FR_CUDA(fr_launch(delta_scan_kernel<TR, DK, true>, grid, block, smem, stream, p));
@@ -360,24 +397,33 @@ int fill_conv(ConvArgs& p, const void* x, int ld, int q_off, int k_off, int v_of
     p.x = x; p.taps_w = taps_w; p.w_dtype = w_dtype; p.out = out; p.state = state; p.state_stride = state_stride;
     p.row_seq = row_seq; p.seq_start = seq_start; p.seq_qlen = seq_qlen; p.seq_slots = seq_slots;
     p.ld = ld; p.q_off = q_off; p.k_off = k_off; p.v_off = v_off; p.qk_heads = qk_heads; p.dk = dk; p.v_channels = v_channels;
-    p.taps = taps; p.rows = rows; p.q_scale = q_scale; p.unit_eps = unit_eps;
+    p.taps = taps; p.rows = rows; p.q_scale = q_scale; p.unit_eps = unit_eps; p.shift = 0;
     return FR_OK;
 }
 
 }  // namespace
 
 // q, k (qk_heads x dk each) and v (v_channels) of x [rows][ld] -> out [rows][2 qk_heads dk + v_channels] fp32.
+// shift_history: only where every sequence of the step brings exactly one row; the state's history then moves on in this
+// kernel and delta_conv_state is not needed.
 FR_EXPORT int delta_conv_prepare(const void* x, int ld, int q_off, int k_off, int v_off, const void* taps_w, int w_dtype, float* out,
                                  const float* state, long long state_stride, const int* row_seq, const int* seq_start,
                                  const int* seq_slots, int rows, int qk_heads, int dk, int v_channels, int taps, float q_scale,
-                                 float unit_eps, int dtype, cudaStream_t stream) {
+                                 float unit_eps, int shift_history, int dtype, cudaStream_t stream) {
     if (rows <= 0) return FR_OK;
     ConvArgs p;
     const int rc = fill_conv(p, x, ld, q_off, k_off, v_off, taps_w, w_dtype, out, (float*)state, state_stride, row_seq, seq_start,
                              nullptr, seq_slots, rows, qk_heads, dk, v_channels, taps, q_scale, unit_eps);
     if (rc != FR_OK) return rc;
-    if (dtype == FR_F32) FR_CUDA(fr_launch(conv_prepare_kernel<float>, dim3(rows), dim3(256), 0, stream, p));
-    else if (dtype == FR_BF16) FR_CUDA(fr_launch(conv_prepare_kernel<bf16>, dim3(rows), dim3(256), 0, stream, p));
+    p.shift = shift_history && taps > 1 ? 1 : 0;
+    int tiles = 1;
+    if (rows < 128) {
+        const int work = (2 * qk_heads + 7) / 8 + (v_channels + 255) / 256;      // rounds of a block's warps and threads
+        tiles = work < 8 ? work : 8;
+        if (tiles < 1) tiles = 1;
+    }
+    if (dtype == FR_F32) FR_CUDA(fr_launch(conv_prepare_kernel<float>, dim3(rows, tiles), dim3(256), 0, stream, p));
+    else if (dtype == FR_BF16) FR_CUDA(fr_launch(conv_prepare_kernel<bf16>, dim3(rows, tiles), dim3(256), 0, stream, p));
     else FR_REFUSE("short convolution: unknown dtype %d", dtype);
     FR_CHECK_LAUNCH("conv_prepare");
     return FR_OK;

@@ -100,20 +100,53 @@ layernorm_cast_kernel(const TI* __restrict__ x, FrVec w, FrVec b, TO* __restrict
     fr_pdl_launch();
     const TI* xr = x + (size_t)blockIdx.x * width;
     TO* yr = y + (size_t)blockIdx.x * width;
+    constexpr int KEEP = 16;                          // rows of up to 4,096 numbers are read once and kept in registers
+    const bool kept = width <= KEEP * (int)blockDim.x;
+    float v[KEEP];
     float sum = 0.f;
-    for (int i = threadIdx.x; i < width; i += blockDim.x) sum += fr_load(xr + i);
+    if (kept) {
+#pragma unroll
+        for (int j = 0; j < KEEP; ++j) {
+            const int i = threadIdx.x + j * blockDim.x;
+            v[j] = i < width ? fr_load(xr + i) : 0.f;
+            sum += v[j];
+        }
+    } else {
+        for (int i = threadIdx.x; i < width; i += blockDim.x) sum += fr_load(xr + i);
+    }
     const float mean = block_sum(sum, partial) / (float)width;
     float ss = 0.f;
-    for (int i = threadIdx.x; i < width; i += blockDim.x) {
-        const float d = fr_load(xr + i) - mean;
-        ss = fmaf(d, d, ss);
+    if (kept) {
+#pragma unroll
+        for (int j = 0; j < KEEP; ++j) {
+            const int i = threadIdx.x + j * blockDim.x;
+            const float d = i < width ? v[j] - mean : 0.f;
+            ss = fmaf(d, d, ss);
+        }
+    } else {
+        for (int i = threadIdx.x; i < width; i += blockDim.x) {
+            const float d = fr_load(xr + i) - mean;
+            ss = fmaf(d, d, ss);
+        }
     }
     ss = block_sum(ss, partial);
     const float inv = 1.0f / sqrtf(ss / (float)width + eps);
-    for (int i = threadIdx.x; i < width; i += blockDim.x) {
-        float v = (fr_load(xr + i) - mean) * inv * w.at(i);
-        if (b.p != nullptr) v += b.at(i);
-        fr_store(yr + i, v);
+    if (kept) {
+#pragma unroll
+        for (int j = 0; j < KEEP; ++j) {
+            const int i = threadIdx.x + j * blockDim.x;
+            if (i < width) {
+                float o = (v[j] - mean) * inv * w.at(i);
+                if (b.p != nullptr) o += b.at(i);
+                fr_store(yr + i, o);
+            }
+        }
+    } else {
+        for (int i = threadIdx.x; i < width; i += blockDim.x) {
+            float o = (fr_load(xr + i) - mean) * inv * w.at(i);
+            if (b.p != nullptr) o += b.at(i);
+            fr_store(yr + i, o);
+        }
     }
 }
 

@@ -83,7 +83,7 @@ struct Recurrence {
 struct Delta {
     last_error_fn last_error;
     int (*conv_prepare)(const void*, int, int, int, int, const void*, int, float*, const float*, long long, const int*, const int*,
-                        const int*, int, int, int, int, int, float, float, int, cudaStream_t);
+                        const int*, int, int, int, int, int, float, float, int, int, cudaStream_t);
     int (*conv_state)(const void*, int, int, int, int, float*, long long, const int*, const int*, const int*, const int*, int, int, int,
                       int, int, int, cudaStream_t);
     int (*scan)(const float*, const void*, int, const void*, int, int, const void*, const void*, int, float*, float*, long long,

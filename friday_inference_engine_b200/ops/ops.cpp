@@ -380,9 +380,9 @@ Tensor Ops::conv_silu_unit(const Tensor& proj, const Tensor& taps, const DeltaSp
     Timed t(*this, Other);
     call(launches_, k, k.conv_prepare(proj.data, (int)proj.ld, (int)s.q_off, (int)s.k_off, (int)s.v_off, taps.data, code(taps.dtype),
                                       (float*)out.data, (const float*)view.state.data, stride, ctx.row_seq, ctx.seq_start, view.seq_slots,
-                                      (int)proj.rows(), s.qk_heads, s.dk, s.heads * s.dv, s.taps, s.q_scale, s.unit_eps, code(proj.dtype),
-                                      stream_), "conv_prepare");
-    if (s.taps > 1)
+                                      (int)proj.rows(), s.qk_heads, s.dk, s.heads * s.dv, s.taps, s.q_scale, s.unit_eps, ctx.decode ? 1 : 0,
+                                      code(proj.dtype), stream_), "conv_prepare");
+    if (s.taps > 1 && !ctx.decode)
         call(launches_, k, k.conv_state(proj.data, (int)proj.ld, (int)s.q_off, (int)s.k_off, (int)s.v_off, (float*)view.state.data, stride,
                                         ctx.row_seq, ctx.seq_start, ctx.seq_qlen, view.seq_slots, ctx.n_seqs, s.qk_heads, s.dk,
                                         s.heads * s.dv, s.taps, code(proj.dtype), stream_), "conv_state");

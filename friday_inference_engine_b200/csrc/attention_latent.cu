@@ -434,23 +434,39 @@ __global__ void __launch_bounds__(128) latent_merge_kernel(AttnArgs p) {
 
 // ------------------------------------------------------------------ prompts: the pieces between tensor-core products
 // Rows [0, n) of one sequence's cached latents and key parts, gathered from the pages into contiguous rows; rows
-// [n, n_pad) are zero.
+// [n, n_pad) are zero.  The latents are written twice, [2 n_pad][rank] with row n_pad + j equal to row j: the values
+// expanded from them then stand side by side twice, once for each half of the split weights.
 template <typename T>
 __global__ void gather_kernel(const T* __restrict__ c_pool, const T* __restrict__ r_pool, const int* __restrict__ table, int page,
-                              int n, int rank, int rot, T* __restrict__ c_all, T* __restrict__ r_all) {
+                              int n, int n_pad, int rank, int rot, T* __restrict__ c_all, T* __restrict__ r_all) {
     fr_pdl_wait();
     fr_pdl_launch();
     const int j = blockIdx.x;
     T* c = c_all + (size_t)j * rank;
+    T* c2 = c_all + (size_t)(n_pad + j) * rank;
     T* r = r_all + (size_t)j * rot;
     if (j >= n) {
-        for (int i = threadIdx.x; i < rank; i += blockDim.x) fr_store(c + i, 0.f);
+        for (int i = threadIdx.x; i < rank; i += blockDim.x) { fr_store(c + i, 0.f); fr_store(c2 + i, 0.f); }
         for (int i = threadIdx.x; i < rot; i += blockDim.x) fr_store(r + i, 0.f);
         return;
     }
     const size_t at = (size_t)table[j / page] * page + j % page;
-    for (int i = threadIdx.x; i < rank; i += blockDim.x) c[i] = c_pool[at * rank + i];
+    for (int i = threadIdx.x; i < rank; i += blockDim.x) { const T v = c_pool[at * rank + i]; c[i] = v; c2[i] = v; }
     for (int i = threadIdx.x; i < rot; i += blockDim.x) r[i] = r_pool[at * rot + i];
+}
+
+// Every head's key [unrotated part from kn [rows][heads * dim] | the shared rotated part r [rows][rot]] side by side:
+// out [rows][heads][dim + rot]
+template <typename T>
+__global__ void key_concat_kernel(const T* __restrict__ kn, const T* __restrict__ r, int heads, int dim, int rot, T* __restrict__ out) {
+    fr_pdl_wait();
+    fr_pdl_launch();
+    const size_t j = blockIdx.x;
+    const int hd = dim + rot;
+    for (int idx = threadIdx.x; idx < heads * hd; idx += blockDim.x) {
+        const int h = idx / hd, e = idx - h * hd;
+        out[j * heads * hd + idx] = e < dim ? kn[j * heads * dim + (size_t)h * dim + e] : r[j * rot + (e - dim)];
+    }
 }
 
 // Row r of scores [rows][ld] (fp32, unscaled) belongs to position pos0 + r and sees keys 0 .. pos0 + r.  Its softmax
@@ -458,7 +474,7 @@ __global__ void gather_kernel(const T* __restrict__ c_pool, const T* __restrict_
 // product with the values keeps the weights' 32-bit precision in effect; keys out of sight get zeros.
 __global__ void __launch_bounds__(256) softmax_split_kernel(const float* __restrict__ s, int ld, int n_pad, int pos0, float scale,
                                                             const void* sink, int sink_dtype, int head, bf16* __restrict__ hi,
-                                                            bf16* __restrict__ lo) {
+                                                            bf16* __restrict__ lo, int ld_p) {
     __shared__ float red[8];
     __shared__ float bc;
     fr_pdl_wait();
@@ -494,8 +510,8 @@ __global__ void __launch_bounds__(256) softmax_split_kernel(const float* __restr
     }
     __syncthreads();
     const float inv = bc;
-    bf16* h = hi + (size_t)row * n_pad;
-    bf16* o = lo + (size_t)row * n_pad;
+    bf16* h = hi + (size_t)row * ld_p;
+    bf16* o = lo + (size_t)row * ld_p;
     for (int j = threadIdx.x; j < n_pad; j += blockDim.x) {
         const float p = j < n ? expf(sr[j] * scale - m) * inv : 0.f;
         const bf16 ph = __float2bfloat16_rn(p);
@@ -592,23 +608,24 @@ FR_EXPORT int attention_latent(const float* q, float* out, const void* c_pool, c
     return FR_OK;
 }
 
-// One sequence's cached rows 0 .. n-1 (table: the sequence's row of the block table) as contiguous [n_pad][rank] and
-// [n_pad][rot]; rows from n on are zero.
+// One sequence's cached rows 0 .. n-1 (table: the sequence's row of the block table) as contiguous [2 n_pad][rank] (the
+// latents twice, one below the other) and [n_pad][rot]; rows from n on are zero.
 FR_EXPORT int attention_latent_gather(const void* c_pool, const void* r_pool, const int* table, int page, int n, int n_pad, int rank,
                                       int rot, void* c_all, void* r_all, int dtype, cudaStream_t stream) {
     if (n_pad <= 0) return FR_OK;
-    if (dtype == FR_F32) FR_CUDA(fr_launch(gather_kernel<float>, dim3(n_pad), dim3(128), 0, stream, (const float*)c_pool, (const float*)r_pool, table, page, n, rank, rot, (float*)c_all, (float*)r_all));
-    else if (dtype == FR_BF16) FR_CUDA(fr_launch(gather_kernel<bf16>, dim3(n_pad), dim3(128), 0, stream, (const bf16*)c_pool, (const bf16*)r_pool, table, page, n, rank, rot, (bf16*)c_all, (bf16*)r_all));
+    if (dtype == FR_F32) FR_CUDA(fr_launch(gather_kernel<float>, dim3(n_pad), dim3(128), 0, stream, (const float*)c_pool, (const float*)r_pool, table, page, n, n_pad, rank, rot, (float*)c_all, (float*)r_all));
+    else if (dtype == FR_BF16) FR_CUDA(fr_launch(gather_kernel<bf16>, dim3(n_pad), dim3(128), 0, stream, (const bf16*)c_pool, (const bf16*)r_pool, table, page, n, n_pad, rank, rot, (bf16*)c_all, (bf16*)r_all));
     else FR_REFUSE("latent gather: unknown dtype %d", dtype);
     FR_CHECK_LAUNCH("latent gather");
     return FR_OK;
 }
 
+// hi and lo: rows of ld_p numbers each (the two may be halves of one buffer's rows)
 FR_EXPORT int attention_latent_softmax_split(const float* scores, int ld, int rows, int n_pad, int pos0, float scale, const void* sink,
-                                             int sink_dtype, int head, void* hi, void* lo, cudaStream_t stream) {
+                                             int sink_dtype, int head, void* hi, void* lo, int ld_p, cudaStream_t stream) {
     if (rows <= 0) return FR_OK;
     FR_CUDA(fr_launch(softmax_split_kernel, dim3(rows), dim3(256), 0, stream, scores, ld, n_pad, pos0, scale, sink, sink_dtype, head,
-                      (bf16*)hi, (bf16*)lo));
+                      (bf16*)hi, (bf16*)lo, ld_p));
     FR_CHECK_LAUNCH("softmax_split");
     return FR_OK;
 }
@@ -620,5 +637,15 @@ FR_EXPORT int attention_latent_gate_cast(const float* x, const void* gate, int l
     else if (dtype == FR_BF16) FR_CUDA(fr_launch(gate_cast_kernel<bf16>, dim3(rows), dim3(256), 0, stream, x, (const bf16*)gate, ld_gate, gate_off, heads, vd, (bf16*)out));
     else FR_REFUSE("gate_cast: unknown dtype %d", dtype);
     FR_CHECK_LAUNCH("gate_cast");
+    return FR_OK;
+}
+
+FR_EXPORT int attention_latent_key_concat(const void* kn, const void* r, int rows, int heads, int dim, int rot, void* out, int dtype,
+                                          cudaStream_t stream) {
+    if (rows <= 0) return FR_OK;
+    if (dtype == FR_F32) FR_CUDA(fr_launch(key_concat_kernel<float>, dim3(rows), dim3(256), 0, stream, (const float*)kn, (const float*)r, heads, dim, rot, (float*)out));
+    else if (dtype == FR_BF16) FR_CUDA(fr_launch(key_concat_kernel<bf16>, dim3(rows), dim3(256), 0, stream, (const bf16*)kn, (const bf16*)r, heads, dim, rot, (bf16*)out));
+    else FR_REFUSE("key_concat: unknown dtype %d", dtype);
+    FR_CHECK_LAUNCH("key_concat");
     return FR_OK;
 }

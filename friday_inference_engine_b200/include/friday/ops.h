@@ -189,8 +189,8 @@ public:
     void head_linear(const Tensor& x, int64_t x_off, int64_t x_stride, const Tensor& w, bool per_head_rows_k, Tensor& out,
                      int64_t out_stride, const Tensor* gate, int64_t gate_off, int heads, int k, int n, const StepContext& ctx);
     // Prompts in bfloat16: the same attention as products on the tensor cores, sequence by sequence and head by head, with keys
-    // and values expanded from the gathered latents: scores = Qn Kn^T + Qr R^T (fp32), a masked softmax with the sink whose
-    // weights are kept as two bf16 numbers each, result = P V.  `proj` holds the queries with their rotated parts already
+    // and values expanded from the gathered latents: scores = Q [Kn | R]^T (fp32), a masked softmax with the sink whose
+    // weights are kept as two bf16 numbers each, result = [P_hi | P_lo] [V; V].  `proj` holds the queries with their rotated parts already
     // rotated; the step's rows are in the cache.  Returns [rows, heads * vdim] in proj's dtype, gates applied.
     Tensor latent_attention_prompt(const Tensor& proj, const Tensor& w_uk, const Tensor& w_uv, const Tensor* sink, const LatentSpec& spec,
                                    const CacheView& view, const StepContext& ctx);

@@ -119,7 +119,8 @@ FAMILY(Delta, delta, "delta", resolve(h, fam, "delta_conv_prepare", t.conv_prepa
 FAMILY(AttentionLatent, attention_latent, "attention_latent", resolve(h, fam, "attention_latent_rotate_pairs", t.rotate_pairs);
        resolve(h, fam, "attention_latent_prepare", t.prepare); resolve(h, fam, "attention_latent_head_linear", t.head_linear);
        resolve(h, fam, "attention_latent", t.run); resolve(h, fam, "attention_latent_gather", t.gather);
-       resolve(h, fam, "attention_latent_softmax_split", t.softmax_split); resolve(h, fam, "attention_latent_gate_cast", t.gate_cast);)
+       resolve(h, fam, "attention_latent_softmax_split", t.softmax_split); resolve(h, fam, "attention_latent_gate_cast", t.gate_cast);
+       resolve(h, fam, "attention_latent_key_concat", t.key_concat);)
 FAMILY(AttentionMma, attention_mma, "attention_mma", resolve(h, fam, "attention_mma", t.run);
        resolve(h, fam, "attention_mma_clusters_at_once", t.clusters_at_once);)
 FAMILY(AttentionTc, attention_tc, "attention_tc", resolve(h, fam, "attention_tc", t.run);)

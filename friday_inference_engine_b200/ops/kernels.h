@@ -99,7 +99,8 @@ struct AttentionLatent {
     int (*run)(const float*, float*, const void*, const void*, const int*, int, int, const int*, const int*, const void*, int, int,
                int, int, int, float, int, float*, int, cudaStream_t);
     int (*gather)(const void*, const void*, const int*, int, int, int, int, int, void*, void*, int, cudaStream_t);
-    int (*softmax_split)(const float*, int, int, int, int, float, const void*, int, int, void*, void*, cudaStream_t);
+    int (*softmax_split)(const float*, int, int, int, int, float, const void*, int, int, void*, void*, int, cudaStream_t);
+    int (*key_concat)(const void*, const void*, int, int, int, int, void*, int, cudaStream_t);
     int (*gate_cast)(const float*, const void*, int, int, int, int, int, void*, int, cudaStream_t);
 };
 struct Routed {

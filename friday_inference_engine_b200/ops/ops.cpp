@@ -472,38 +472,41 @@ Tensor Ops::latent_attention_prompt(const Tensor& proj, const Tensor& w_uk, cons
     for (int q = 0; q < ctx.n_seqs; ++q) {
         const int64_t T = ctx.q_lens[(size_t)q], n = ctx.kv_lens[(size_t)q], n_pad = (n + 7) / 8 * 8;
         if (T <= 0) continue;
-        Tensor c_all = alloc(DType::BF16, n_pad, s.rank), r_all = alloc(DType::BF16, n_pad, s.rot);
+        Tensor c_all = alloc(DType::BF16, 2 * n_pad, s.rank), r_all = alloc(DType::BF16, n_pad, s.rot);
         {
             Timed t(*this, Attention);
             call(launches_, k, k.gather(view.k_pool, view.v_pool, view.block_table + (size_t)q * view.table_width, view.page_size, (int)n,
                                         (int)n_pad, s.rank, s.rot, c_all.data, r_all.data, code(DType::BF16), stream_), "latent gather");
         }
-        Tensor kn = linear(Rows(c_all), w_uk);                     // [n_pad, heads * dim]: every head's unrotated keys
-        Tensor vt = linear(Rows(w_uv), c_all);                     // [heads * vdim, n_pad]: every head's values, transposed
+        const int64_t hd = (int64_t)s.dim + s.rot;
+        Tensor kn = linear(Rows(c_all.row_slice(0, n_pad)), w_uk);      // [n_pad, heads * dim]: every head's unrotated keys
+        Tensor kcat = alloc(DType::BF16, n_pad, s.heads * hd);          // [n_pad, heads, dim + rot]: whole keys, head by head
+        {
+            Timed t(*this, Attention);
+            call(launches_, k, k.key_concat(kn.data, r_all.data, (int)n_pad, s.heads, s.dim, s.rot, kcat.data, code(DType::BF16), stream_),
+                 "key_concat");
+        }
+        Tensor vt = linear(Rows(w_uv), c_all);                          // [heads * vdim, 2 n_pad]: values, transposed, twice side by side
         Tensor scores = alloc(DType::F32, T, n_pad);
-        Tensor p_hi = alloc(DType::BF16, T, n_pad), p_lo = alloc(DType::BF16, T, n_pad);
+        Tensor weights = alloc(DType::BF16, T, 2 * n_pad);              // every weight as two bf16 numbers: [hi | lo]
         const Tensor rows = proj.row_slice(r0, T);
         for (int h = 0; h < s.heads; ++h) {
-            Tensor qn = rows, qr = rows, kh = kn, vh = vt.row_slice((int64_t)h * s.vdim, s.vdim);
-            qn.data = (char*)rows.data + (size_t)(s.q_off + (int64_t)h * (s.dim + s.rot)) * 2;
-            qn.shape[1] = s.dim;
-            qr.data = (char*)qn.data + (size_t)s.dim * 2;
-            qr.shape[1] = s.rot;
-            kh.data = (char*)kn.data + (size_t)h * s.dim * 2;
-            kh.shape[1] = s.dim;
-            linear(Rows(qn), kh, nullptr, nullptr, (int)DType::F32, &scores);
-            linear(Rows(qr), r_all, nullptr, &scores, (int)DType::F32, &scores);
+            Tensor qh = rows, kh = kcat, vh = vt.row_slice((int64_t)h * s.vdim, s.vdim);
+            qh.data = (char*)rows.data + (size_t)(s.q_off + (int64_t)h * hd) * 2;
+            qh.shape[1] = hd;
+            kh.data = (char*)kcat.data + (size_t)h * hd * 2;
+            kh.shape[1] = hd;
+            linear(Rows(qh), kh, nullptr, nullptr, (int)DType::F32, &scores);
             {
                 Timed t(*this, Attention);
                 call(launches_, k, k.softmax_split((const float*)scores.data, (int)scores.ld, (int)T, (int)n_pad, (int)(n - T), s.scale,
-                                                   sink ? sink->data : nullptr, sink ? code(sink->dtype) : 0, h, p_hi.data, p_lo.data,
-                                                   stream_), "softmax_split");
+                                                   sink ? sink->data : nullptr, sink ? code(sink->dtype) : 0, h, weights.data,
+                                                   (char*)weights.data + (size_t)n_pad * 2, (int)(2 * n_pad), stream_), "softmax_split");
             }
             Tensor oh = of.row_slice(r0, T);
             oh.data = (char*)oh.data + (size_t)h * s.vdim * 4;
             oh.shape[1] = s.vdim;
-            linear(Rows(p_hi), vh, nullptr, nullptr, (int)DType::F32, &oh);
-            linear(Rows(p_lo), vh, nullptr, &oh, (int)DType::F32, &oh);
+            linear(Rows(weights), vh, nullptr, nullptr, (int)DType::F32, &oh);
         }
         r0 += T;
     }

@@ -69,6 +69,11 @@ CONFIGS = {
     "S": (config(100, 333, [delta(6, 2, 24, 40, 3, channel=True), latent(5, 24, 6, 40, 50, 777.0, (2.0, 100, 8.0, 0.5)),
                             delta(3, 1, 40, 24, 6)],
                  [56, 6, 30], loop=(0, 3, 1), scale=0.5), {"l0": (6, 10)}),
+    # sizes that nothing divides: key channels of 10 and 6, value channels of 12 and 5, an odd latent, eight taps, five heads
+    # on five and on one query/key head, a width that is a multiple of 4 only
+    "T": (config(52, 97, [delta(5, 5, 10, 12, 8), latent(3, 10, 6, 7, 17, 300.0, (3.0, 50, 4.0, 0.25), 0.4),
+                          delta(5, 1, 6, 5, 2, channel=True)],
+                 [10, 22, None], loop=(1, 2, 2), scale=1.7), {"l2": (3, 5)}),
     # single mechanisms
     "delta_only": (config(64, 100, [delta(4, 2, 16, 24, 4)], [None]), {}),
     "channel_only": (config(64, 100, [delta(2, 1, 16, 24, 3, channel=True)], [None]), {"l0": (4, 6)}),
@@ -218,7 +223,7 @@ def test_each_mechanism_alone(root, name, dtype):
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
-@pytest.mark.parametrize("name,n", [("P", 150), ("Q", 70), ("R", 300), ("S", 200)])
+@pytest.mark.parametrize("name,n", [("P", 150), ("Q", 70), ("R", 300), ("S", 200), ("T", 130)])
 def test_whole_prompt(root, name, n, dtype):
     eng, cfg, _ = engine(root, name, dtype)
     (p,) = prompts([n], cfg["vocab"], 5)
@@ -256,7 +261,7 @@ def test_faults_would_show(root):
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
-@pytest.mark.parametrize("name", ["P", "R", "S"])
+@pytest.mark.parametrize("name", ["P", "R", "S", "T"])
 def test_prompt_then_token_by_token(root, name, dtype):
     """The last tokens one by one, across page borders of 64: states, the convolution's history and the cached latents
     go from step to step."""
@@ -286,7 +291,7 @@ def test_all_tokens_one_by_one(root, name, dtype):
 
 @pytest.mark.parametrize("dtype", DTYPES)
 @pytest.mark.parametrize("name,cuts", [("P", [2, 3, 7, 64, 65, 9, 1, 1, 2]), ("R", [64, 2, 128, 100, 6]), ("Q", [1, 2, 30, 37, 3]),
-                                       ("S", [5, 64, 3, 70, 2, 2])])
+                                       ("S", [5, 64, 3, 70, 2, 2]), ("T", [3, 2, 40, 1, 5, 66, 2])])
 def test_portions(root, name, cuts, dtype):
     """A prompt cut into steps of several sizes, down to two tokens (and one): portions shorter than the convolution
     keep part of the history that was there."""

@@ -56,8 +56,8 @@ void check_latent(const Json& m, const std::string& where) {
     const Json& rot = member(m, "rot", where);
     const std::string rw = where + "rot: ";
     if (!(number(rot, "base", rw) > 1.0)) throw ConfigError("config.json: " + rw + "'base' must be greater than 1");
-    if (positive_int(rot, "dims", rw) != rd) throw ConfigError("config.json: " + rw + "'dims' must equal the mixer's 'rot_dim'");
-    if (rd % 2) throw ConfigError("config.json: " + where + "'rot_dim' must be even");
+    const int64_t dims = positive_int(rot, "dims", rw);
+    if (dims > rd || dims % 2) throw ConfigError("config.json: " + rw + "'dims' must be even and at most the mixer's 'rot_dim'");
     const Json* sc = rot.find("scaling");
     if (sc && !sc->is_null())
         for (const char* k : {"factor", "original", "fast", "slow"})

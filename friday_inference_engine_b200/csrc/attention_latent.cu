@@ -76,6 +76,7 @@ struct PrepareArgs {
     const float* freq;        // [rot / 2]
     float mult, eps;
     int ld, q_off, kv_off, heads, dim, rot, rank;
+    int rot_dims;             // the first rot_dims of the rot numbers turn, the rest pass unchanged
 };
 
 template <typename T>
@@ -101,7 +102,14 @@ __global__ void __launch_bounds__(256) prepare_kernel(PrepareArgs p) {
     const FrVec w{p.norm_w, p.norm_dtype};
     for (int i = threadIdx.x; i < p.rank; i += blockDim.x) fr_store(ckr + i, fr_load(x + p.kv_off + i) * inv * w.at(i));
     const float pos = (float)p.row_pos[row];
-    const int half = p.rot / 2;
+    const int half = p.rot_dims / 2;
+    // what does not turn passes as it is
+    const int still = p.rot - p.rot_dims;
+    for (int idx = threadIdx.x; idx < (p.heads + 1) * still; idx += blockDim.x) {
+        const int item = idx / still, e = p.rot_dims + (idx - item * still);
+        if (item == 0) ckr[p.rank + e] = x[p.kv_off + p.rank + e];
+        else p.qf[((size_t)row * p.heads + item - 1) * (p.rank + p.rot) + p.rank + e] = fr_load(x + p.q_off + (size_t)(item - 1) * (p.dim + p.rot) + p.dim + e);
+    }
     // the key part (item 0) and every head's rotated query part
     for (int idx = threadIdx.x; idx < (p.heads + 1) * half; idx += blockDim.x) {
         const int item = idx / half, i = idx - item * half;
@@ -551,10 +559,12 @@ FR_EXPORT int attention_latent_rotate_pairs(void* x, int ld, const int* row_seq,
 
 FR_EXPORT int attention_latent_prepare(const void* x, int ld, int q_off, int kv_off, void* ckr, float* qf, const void* norm_w,
                                        int norm_dtype, float eps, const int* row_seq, const int* row_pos, const float* freq,
-                                       float mult, int rows, int heads, int dim, int rot, int rank, int dtype, cudaStream_t stream) {
+                                       float mult, int rows, int heads, int dim, int rot, int rot_dims, int rank, int dtype,
+                                       cudaStream_t stream) {
     if (rows <= 0) return FR_OK;
-    if (rot % 2 || rot < 0 || rank <= 0 || heads <= 0) FR_REFUSE("latent prepare: rank %d, rotated part %d, %d heads", rank, rot, heads);
-    PrepareArgs p{x, ckr, qf, norm_w, norm_dtype, row_seq, row_pos, freq, mult, eps, ld, q_off, kv_off, heads, dim, rot, rank};
+    if (rot_dims % 2 || rot_dims < 0 || rot_dims > rot || rank <= 0 || heads <= 0)
+        FR_REFUSE("latent prepare: rank %d, rotated part %d of which %d turn, %d heads", rank, rot, rot_dims, heads);
+    PrepareArgs p{x, ckr, qf, norm_w, norm_dtype, row_seq, row_pos, freq, mult, eps, ld, q_off, kv_off, heads, dim, rot, rank, rot_dims};
     if (dtype == FR_F32) FR_CUDA(fr_launch(prepare_kernel<float>, dim3(rows), dim3(256), 0, stream, p));
     else if (dtype == FR_BF16) FR_CUDA(fr_launch(prepare_kernel<bf16>, dim3(rows), dim3(256), 0, stream, p));
     else FR_REFUSE("latent prepare: unknown dtype %d", dtype);

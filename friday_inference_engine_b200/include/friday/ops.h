@@ -175,6 +175,7 @@ public:
     // ---- attention over a cached latent (csrc/attention_latent.cu)
     struct LatentSpec {
         int heads = 0, dim = 0, rot = 0, rank = 0, vdim = 0;
+        int rot_dims = 0;               // how many of the rot numbers turn (the first ones; 0: all)
         float scale = 1.f, eps = 1e-5f, rot_mult = 1.f;
         const float* freq = nullptr;    // device: rot / 2 angular frequencies
         int64_t q_off = 0, kv_off = 0, gate_off = -1;   // columns of the stacked projection: queries, [latent | key part], gates

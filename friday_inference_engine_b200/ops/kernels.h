@@ -93,7 +93,7 @@ struct AttentionLatent {
     last_error_fn last_error;
     int (*rotate_pairs)(void*, int, const int*, const int*, const float*, float, int, int, int, int, int, int, cudaStream_t);
     int (*prepare)(const void*, int, int, int, void*, float*, const void*, int, float, const int*, const int*, const float*, float, int,
-                   int, int, int, int, int, cudaStream_t);
+                   int, int, int, int, int, int, cudaStream_t);
     int (*head_linear)(const void*, int, int, int, int, const void*, int, int, void*, int, int, int, const void*, int, int, const int*,
                        int, int, int, int, cudaStream_t);
     int (*run)(const float*, float*, const void*, const void*, const int*, int, int, const int*, const int*, const void*, int, int,

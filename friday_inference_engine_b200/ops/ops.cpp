@@ -428,7 +428,7 @@ Tensor Ops::latent_prepare(const Tensor& proj, const Tensor& norm_w, const Laten
     Timed t(*this, Other);
     call(launches_, k, k.prepare(proj.data, (int)proj.ld, (int)s.q_off, (int)s.kv_off, ckr.data, (float*)qf.data, norm_w.data,
                                  code(norm_w.dtype), s.eps, ctx.row_seq, ctx.row_pos, s.freq, s.rot_mult, (int)proj.rows(), s.heads, s.dim,
-                                 s.rot, s.rank, code(proj.dtype), stream_), "latent_prepare");
+                                 s.rot, s.rot_dims > 0 ? s.rot_dims : s.rot, s.rank, code(proj.dtype), stream_), "latent_prepare");
     return ckr;
 }
 

@@ -9,7 +9,7 @@
 //                              o / rms_head(o) * norm * gate, gate = silu(Wg h) or sigmoid(Wg2 (Wg1 h)) ("gate": "low_rank");
 //                              then Wo.  State per sequence: the convolution's last taps-1 inputs, then the heads' matrices.
 //   mixer "latent_attention"   q = Wq h (heads x [dim | rot]); Wdkv h = [latent (rank) | key part (rot)]; the latent is
-//                              RMS-normed; query and key parts of size rot are rotated by the position part; per head the
+//                              RMS-normed; query and key parts of size rot are rotated by the position part (its first `dims` numbers, if fewer); per head the
 //                              key is [Wuk latent | key part], the value Wuv latent; causal softmax with a sink per head in
 //                              the denominator; every head's result times sigmoid(Wg h)_head; then Wo.  The cache keeps the
 //                              normed latent and the rotated key part, nothing per head.
@@ -174,9 +174,8 @@ public:
     void finalize(Ops& ops) override {
         Mixer::finalize(ops);
         if (rot_ > 0) {
-            int dims = 0;
-            if (!position_->pairs(&freq_, &mult_, &dims) || dims != rot_)
-                throw ConfigError(prefix + ": latent_attention needs a position part that rotates neighbouring pairs over exactly its rotated size");
+            if (!position_->pairs(&freq_, &mult_, &rot_dims_) || rot_dims_ > rot_ || rot_dims_ % 2)
+                throw ConfigError(prefix + ": latent_attention needs a position part that rotates neighbouring pairs of at most its rotated size");
         }
     }
 
@@ -194,6 +193,7 @@ public:
         sp.scale = scale_;
         sp.eps = eps_;
         sp.rot_mult = mult_;
+        sp.rot_dims = rot_dims_;
         sp.freq = freq_;
         sp.q_off = 0;
         sp.kv_off = qd;
@@ -206,7 +206,7 @@ public:
         const char* tc = getenv("FRIDAY_LATENT_TC");
         if (x.dtype == DType::BF16 && view.dtype == DType::BF16 && !ctx.decode && ctx.max_q_len >= 32 && (int)ctx.q_lens.size() == ctx.n_seqs &&
             dim_ % 8 == 0 && rot_ % 8 == 0 && vdim_ % 8 == 0 && rank_ % 8 == 0 && !(tc && tc[0] == '0')) {
-            ops.rotate_pairs(in, ctx, freq_, mult_, heads_, dim_ + rot_, dim_, rot_);
+            ops.rotate_pairs(in, ctx, freq_, mult_, heads_, dim_ + rot_, dim_, rot_dims_);
             Tensor mixed = ops.latent_attention_prompt(in, tensor("uk"), tensor("uv"), has_sink_ ? &tensor("sink") : nullptr, sp, view, ctx);
             return PartOut(ops.linear_residual(Rows(mixed), tensor("o"), nullptr, residual, out_scale));
         }
@@ -219,7 +219,7 @@ public:
     }
 
 private:
-    int heads_, dim_, rot_, vdim_, rank_;
+    int heads_, dim_, rot_, vdim_, rank_, rot_dims_ = 0;
     int64_t in_rows_;
     float eps_, scale_, mult_ = 1.0f;
     bool has_sink_, has_gate_;

@@ -29,8 +29,8 @@ pytestmark = pytest.mark.gpu
 DTYPES = [pytest.param("float32", id="f32"), pytest.param("bfloat16", id="bf16")]
 
 
-def latent(heads, dim, rot, vdim, rank, base=10000.0, scaling=None, scale=None):
-    rot_spec = {"base": base, "dims": rot}
+def latent(heads, dim, rot, vdim, rank, base=10000.0, scaling=None, scale=None, turning=None):
+    rot_spec = {"base": base, "dims": turning or rot}
     if scaling:
         rot_spec["scaling"] = dict(zip(("factor", "original", "fast", "slow"), scaling))
     return {"type": "latent_attention",
@@ -62,16 +62,16 @@ CONFIGS = {
                  [16, None, 32]), {"l2": (3, 2)}),
     # sizes that the tensor-core products like; prompts of several pages; a loop of the first layers run twice
     "R": (config(128, 512, [latent(4, 32, 32, 64, 64, 20000.0, (4.0, 256, 32.0, 1.0), 0.11), delta(4, 2, 32, 32, 4),
-                            delta(4, 4, 64, 32, 3, channel=True), latent(2, 64, 16, 32, 96, 1000.0)],
+                            delta(4, 4, 64, 32, 3, channel=True), latent(2, 64, 16, 32, 96, 1000.0, turning=8)],
                  [128, 64, 128, None], loop=(0, 2, 2), scale=11.3), {"l2": (16, 8)}),
     # sizes that fit no tile: a width that is no multiple of 8 (no tensor-core product at all), odd head sizes, a latent
     # that no warp divides, a loop that is run once
     "S": (config(100, 333, [delta(6, 2, 24, 40, 3, channel=True), latent(5, 24, 6, 40, 50, 777.0, (2.0, 100, 8.0, 0.5)),
                             delta(3, 1, 40, 24, 6)],
                  [56, 6, 30], loop=(0, 3, 1), scale=0.5), {"l0": (6, 10)}),
-    # sizes that nothing divides: key channels of 10 and 6, value channels of 12 and 5, an odd latent, eight taps, five heads
+    # sizes that nothing divides (and a rotated part of which only the first four numbers turn): key channels of 10 and 6, value channels of 12 and 5, an odd latent, eight taps, five heads
     # on five and on one query/key head, a width that is a multiple of 4 only
-    "T": (config(52, 97, [delta(5, 5, 10, 12, 8), latent(3, 10, 6, 7, 17, 300.0, (3.0, 50, 4.0, 0.25), 0.4),
+    "T": (config(52, 97, [delta(5, 5, 10, 12, 8), latent(3, 10, 6, 7, 17, 300.0, (3.0, 50, 4.0, 0.25), 0.4, turning=4),
                           delta(5, 1, 6, 5, 2, channel=True)],
                  [10, 22, None], loop=(1, 2, 2), scale=1.7), {"l2": (3, 5)}),
     # single mechanisms

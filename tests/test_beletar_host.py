@@ -72,7 +72,8 @@ def test_declared_tensors():
     (lambda c: c["layers"][0]["mixer"].update(kv_heads=3), "share"),
     (lambda c: c["layers"][0]["mixer"].update(conv=9), "conv"),
     (lambda c: c["layers"][1]["mixer"].pop("kv_rank"), "kv_rank"),
-    (lambda c: c["layers"][1]["mixer"]["rot"].update(dims=6), "dims"),
+    (lambda c: c["layers"][1]["mixer"]["rot"].update(dims=10), "dims"),
+    (lambda c: c["layers"][1]["mixer"]["rot"].update(dims=3), "dims"),
     (lambda c: c["layers"][1]["mixer"]["rot"]["scaling"].update(factor=0), "factor"),
     (lambda c: c["loop"].update(stop=9), "loop"),
 ])

@@ -63,8 +63,7 @@ public:
         if (dk_ > 256) throw ConfigError("gated_delta: at most 256 key channels per head");
         const int64_t w = e.width, qk = (int64_t)qk_heads_ * dk_, hv = (int64_t)heads_ * dv_;
         // one product for everything in the activation dtype: q, k, v (and the full gate)
-        main_rows_ = 2 * qk + hv + (low_rank_gate_ ? 0 : hv);
-        declare_stacked("w_in", main_rows_, w);
+        declare_stacked("w_in", 2 * qk + hv + (low_rank_gate_ ? 0 : hv), w);
         declare("q", {qk, w}).stack("w_in", 0);
         declare("k", {qk, w}).stack("w_in", qk);
         declare("v", {hv, w}).stack("w_in", 2 * qk);
@@ -75,8 +74,7 @@ public:
         declare("k.conv", {qk, (int64_t)taps_}).stack("taps", qk);
         declare("v.conv", {hv, (int64_t)taps_}).stack("taps", 2 * qk);
         // what enters the recurrence: beta (and the per-head decay) in one product whose result stays 32-bit
-        small_rows_ = heads_ + (per_channel_ ? 0 : heads_);
-        declare_stacked("w_rec", small_rows_, w);
+        declare_stacked("w_rec", heads_ + (per_channel_ ? 0 : heads_), w);
         declare("b", {(int64_t)heads_, w}).stack("w_rec", 0);
         if (!per_channel_) declare("a", {(int64_t)heads_, w}).stack("w_rec", heads_);
         // the inner sizes of the two-step projections are the checkpoint's to give unless "decay_rank" / "gate_rank" name them
@@ -135,7 +133,6 @@ public:
 
 private:
     int heads_, qk_heads_, dk_, dv_, taps_;
-    int64_t main_rows_, small_rows_;
     float eps_;
     bool per_channel_, low_rank_gate_;
 };
@@ -158,8 +155,7 @@ public:
         if ((int64_t)rank_ * 8 * 4 > 48 * 1024 || (int64_t)dim_ * 8 * 4 > 48 * 1024) throw ConfigError("latent_attention: head sizes beyond what the per-head products stage");
         position_ = adopt("", build<Position>("position", s.part("position"), e));
         const int64_t w = e.width, qd = (int64_t)heads_ * (dim_ + rot_), kvd = (int64_t)rank_ + rot_;
-        in_rows_ = qd + kvd + (has_gate_ ? heads_ : 0);
-        declare_stacked("w_in", in_rows_, w);
+        declare_stacked("w_in", qd + kvd + (has_gate_ ? heads_ : 0), w);
         declare("q", {qd, w}).stack("w_in", 0);
         declare("dkv", {kvd, w}).stack("w_in", qd);
         if (has_gate_) declare("g", {(int64_t)heads_, w}).stack("w_in", qd + kvd);
@@ -220,7 +216,6 @@ public:
 
 private:
     int heads_, dim_, rot_, vdim_, rank_, rot_dims_ = 0;
-    int64_t in_rows_;
     float eps_, scale_, mult_ = 1.0f;
     bool has_sink_, has_gate_;
     Position* position_;

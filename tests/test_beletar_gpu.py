@@ -74,6 +74,10 @@ CONFIGS = {
     "T": (config(52, 97, [delta(5, 5, 10, 12, 8), latent(3, 10, 6, 7, 17, 300.0, (3.0, 50, 4.0, 0.25), 0.4, turning=4),
                           delta(5, 1, 6, 5, 2, channel=True)],
                  [10, 22, None], loop=(1, 2, 2), scale=1.7), {"l2": (3, 5)}),
+    # heads as large as real models have them: key channels of 128 and 256, a latent of 512 with a rotated part of 64
+    "U": (config(256, 200, [delta(2, 1, 128, 128, 4), latent(2, 128, 64, 128, 512, 10000.0, (4.0, 128, 32.0, 1.0)),
+                            delta(2, 2, 256, 64, 4, channel=True)],
+                 [64, None, 64], loop=(0, 3, 2), scale=4.0), {"l2": (16, 16)}),
     # single mechanisms
     "delta_only": (config(64, 100, [delta(4, 2, 16, 24, 4)], [None]), {}),
     "channel_only": (config(64, 100, [delta(2, 1, 16, 24, 3, channel=True)], [None]), {"l0": (4, 6)}),
@@ -101,10 +105,11 @@ def tensors_of(cfg, ranks, rng):
         out[p + "norm1.b"] = normal((w,), 0.2)
         if L["type"] == "latent_attention":
             H, dim, rd, vd, rank = m["heads"], m["dim"], m["rot_dim"], m["vdim"], m["kv_rank"]
-            out[p + "mix.q"] = normal((H * (dim + rd), w), 0.5)
-            out[p + "mix.dkv"] = normal((rank + rd, w), 0.3)
+            # scores of a few units whatever the sizes: peaked, but not so that two keys within rounding of each other swap
+            out[p + "mix.q"] = normal((H * (dim + rd), w), 0.5 * min(1.0, (32.0 / (dim + rd)) ** 0.5) * min(1.0, (96.0 / w) ** 0.5))
+            out[p + "mix.dkv"] = normal((rank + rd, w), 0.3 * min(1.0, (96.0 / w) ** 0.5))
             out[p + "mix.dkv.norm"] = normal((rank,), 0.1, 1.0)
-            out[p + "mix.uk"] = normal((H * dim, rank), 0.3)
+            out[p + "mix.uk"] = normal((H * dim, rank), 0.3 * min(1.0, (64.0 / rank) ** 0.5))
             out[p + "mix.uv"] = normal((H * vd, rank), 0.1)
             out[p + "mix.sink"] = normal((H,), 2.0, 1.0)
             out[p + "mix.g"] = normal((H, w), 0.2)
@@ -223,7 +228,7 @@ def test_each_mechanism_alone(root, name, dtype):
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
-@pytest.mark.parametrize("name,n", [("P", 150), ("Q", 70), ("R", 300), ("S", 200), ("T", 130)])
+@pytest.mark.parametrize("name,n", [("P", 150), ("Q", 70), ("R", 300), ("S", 200), ("T", 130), ("U", 100)])
 def test_whole_prompt(root, name, n, dtype):
     eng, cfg, _ = engine(root, name, dtype)
     (p,) = prompts([n], cfg["vocab"], 5)
@@ -261,7 +266,7 @@ def test_faults_would_show(root):
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
-@pytest.mark.parametrize("name", ["P", "R", "S", "T"])
+@pytest.mark.parametrize("name", ["P", "R", "S", "T", "U"])
 def test_prompt_then_token_by_token(root, name, dtype):
     """The last tokens one by one, across page borders of 64: states, the convolution's history and the cached latents
     go from step to step."""

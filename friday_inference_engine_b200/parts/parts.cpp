@@ -265,11 +265,13 @@ public:
 };
 
 // ------------------------------------------------------------------ rotary encoding, neighbouring pairs
-// The pair (2i, 2i + 1) of the first `dims` dimensions turns by pos * f_i, f_i = base^(-2i / dims).  With "scaling"
-// {factor, original, fast, slow} long wavelengths are stretched: with dim(t) = dims ln(original / (2 pi t)) / (2 ln base),
-// lo = max(floor(dim(fast)), 0), hi = min(ceil(dim(slow)), dims - 1) and ramp_i = clamp((i - lo) / max(hi - lo, 0.001), 0, 1)
-// the frequency is f_i / factor * ramp_i + f_i (1 - ramp_i), and cosine and sine are multiplied by 0.1 ln(factor) + 1.
-// The table is made once on the host in double precision and rounded to fp32; the angle is fp32(pos) * f_i in the kernel.
+// Neighbours (2i, 2i + 1) among the first `dims` numbers of a head turn by the angle pos * w_i, w_i = base^(-2i / dims).
+// "scaling" {factor, original, fast, slow} stretches the long wavelengths: a pair that completes t turns within
+// `original` positions has index d(t) = dims * ln(original / (2 pi t)) / (2 ln base); pairs up to index
+// first = max(floor(d(fast)), 0) keep their w_i, pairs from last = min(ceil(d(slow)), dims - 1) on turn `factor` times
+// slower, and between the two the mix moves linearly, mix_i = clamp((i - first) / max(last - first, 0.001), 0, 1):
+// w_i <- (1 - mix_i) w_i + mix_i w_i / factor.  Cosine and sine are then multiplied by 1 + 0.1 ln(factor).
+// The table is made once on the host in double precision and rounded to fp32; the angle is fp32(pos) * w_i in the kernel.
 class RotaryPairs : public Position {
 public:
     RotaryPairs(const PartSpec& s, const BuildEnv& e) : Position(e) {
@@ -288,11 +290,11 @@ public:
             if (!(factor > 0) || !(original > 0) || !(fast > 0) || !(slow > 0))
                 throw ConfigError("rotary_pairs: 'scaling' needs positive factor, original, fast and slow");
             auto dim_of = [&](double turns) { return dims_ * log(original / (2.0 * M_PI * turns)) / (2.0 * log(base)); };
-            const double lo = std::max(floor(dim_of(fast)), 0.0), hi = std::min(ceil(dim_of(slow)), (double)dims_ - 1.0);
+            const double first = std::max(floor(dim_of(fast)), 0.0), last = std::min(ceil(dim_of(slow)), (double)dims_ - 1.0);
             for (int i = 0; i < half; ++i) {
-                double ramp = ((double)i - lo) / std::max(hi - lo, 0.001);
-                ramp = ramp < 0 ? 0 : (ramp > 1 ? 1 : ramp);
-                f[i] = f[i] / factor * ramp + f[i] * (1.0 - ramp);
+                double mix = ((double)i - first) / std::max(last - first, 0.001);
+                mix = mix < 0 ? 0 : (mix > 1 ? 1 : mix);
+                f[i] = f[i] / factor * mix + f[i] * (1.0 - mix);
             }
             mult_ = (float)(0.1 * log(factor) + 1.0);
         }
